@@ -1,0 +1,206 @@
+// extern "C" entry points declared in include/b200_lora.h: argument checks and launches only.
+#include <string.h>
+
+#include "lora_common.cuh"
+
+using namespace b200lora;
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int cuda_fail(cudaError_t e) {
+    strncpy(g_last_error, cudaGetErrorString(e), sizeof(g_last_error) - 1);
+    return B200_LORA_ERR_CUDA;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_adapters(const b200_lora_adapters* ad) {
+    if (!ad) return B200_LORA_ERR_NULL;
+    if (ad->n_adapters < 1 || ad->n_layers < 1) return B200_LORA_ERR_DIM;
+    if (ad->r_pool < 1 || ad->r_pool > kMaxRank) return B200_LORA_ERR_RANK;
+    if (ad->packed) {
+        if (!ad->cum_ranks || !ad->ranks) return B200_LORA_ERR_NULL;
+    } else if (ad->r_pool % 8) {
+        return B200_LORA_ERR_RANK;     // rows of the dense B pool must stay 16-byte aligned
+    }
+    return B200_LORA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_lora_arch(void) { return 100; }
+
+const char* b200_lora_last_cuda_error(void) { return g_last_error; }
+
+size_t b200_lora_plan_bytes(int32_t max_tokens, int32_t n_adapters) {
+    if (max_tokens < 1 || n_adapters < 1) return 0;
+    return plan_words(max_tokens, n_adapters) * 4;
+}
+
+int b200_lora_plan_build(void* plan, size_t plan_bytes, int32_t max_tokens, const void* ids,
+                         int32_t ids_are_i64, int32_t n_tokens, const b200_lora_adapters* adapters,
+                         void* stream) {
+    if (!plan || !ids) return B200_LORA_ERR_NULL;
+    int rc = check_adapters(adapters);
+    if (rc) return rc;
+    if (n_tokens < 1 || n_tokens > max_tokens) return B200_LORA_ERR_DIM;
+    const int cap = max_tokens;
+    if (plan_bytes < b200_lora_plan_bytes(cap, adapters->n_adapters)) return B200_LORA_ERR_WORKSPACE;
+    if (!aligned16(plan)) return B200_LORA_ERR_ALIGN;
+    cudaError_t e = launch_plan_build(plan, cap, ids, ids_are_i64, n_tokens, adapters->ranks, adapters->r_pool,
+                                      adapters->n_adapters, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_plan_from_segments(void* plan, size_t plan_bytes, int32_t max_tokens,
+                                 const int32_t* seg_starts, const int32_t* seg_adapter, int32_t n_segs,
+                                 int32_t n_tokens, const b200_lora_adapters* adapters, void* stream) {
+    if (!plan || !seg_starts || !seg_adapter) return B200_LORA_ERR_NULL;
+    int rc = check_adapters(adapters);
+    if (rc) return rc;
+    if (n_tokens < 1 || n_tokens > max_tokens || n_segs < 1 || n_segs > n_tokens) return B200_LORA_ERR_DIM;
+    const int cap = max_tokens;
+    if (plan_bytes < b200_lora_plan_bytes(cap, adapters->n_adapters)) return B200_LORA_ERR_WORKSPACE;
+    if (!aligned16(plan)) return B200_LORA_ERR_ALIGN;
+    cudaError_t e = launch_plan_from_segments(plan, cap, seg_starts, seg_adapter, n_segs, n_tokens,
+                                              adapters->ranks, adapters->r_pool, adapters->n_adapters,
+                                              static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_plan_read(const void* plan, int32_t* perm, int32_t* seg_starts, int32_t* seg_adapter,
+                        int32_t* n_segs, int32_t* n_tokens, void* stream) {
+    if (!plan || !n_segs || !n_tokens) return B200_LORA_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PlanHeader h;
+    cudaError_t e = cudaMemcpyAsync(&h, plan, sizeof(h), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    *n_segs = h.n_segs;
+    *n_tokens = h.n_tokens;
+    if (h.error == 1) return B200_LORA_ERR_ID_RANGE;
+    if (h.error) return B200_LORA_ERR_SEGMENTS;
+    PlanView pv = plan_view(const_cast<void*>(plan), h.cap, h.n_adapters);
+    if (perm) e = cudaMemcpyAsync(perm, pv.perm, 4 * (size_t)h.n_tokens, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess && seg_starts)
+        e = cudaMemcpyAsync(seg_starts, pv.seg_start, 4 * (size_t)(h.n_segs + 1), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess && seg_adapter)
+        e = cudaMemcpyAsync(seg_adapter, pv.seg_adapter, 4 * (size_t)h.n_segs, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+size_t b200_lora_workspace_bytes(int32_t max_tokens, int32_t n_proj, int32_t max_h_in) {
+    if (max_tokens < 1 || n_proj < 1 || n_proj > kMaxProj || max_h_in < 8) return 0;
+    return workspace_bytes(max_tokens, n_proj, max_h_in);
+}
+
+int b200_lora_workspace_init(void* workspace, size_t bytes, void* stream) {
+    if (!workspace) return B200_LORA_ERR_NULL;
+    if (bytes < sizeof(WorkspaceCtl)) return B200_LORA_ERR_WORKSPACE;
+    cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
+                    const void* plan, int32_t max_tokens, int32_t layer, int32_t io_dtype, int32_t y_dtype,
+                    int32_t flags, void* workspace, size_t workspace_bytes_, void* stream) {
+    if (!projs || !plan || !workspace) return B200_LORA_ERR_NULL;
+    int rc = check_adapters(adapters);
+    if (rc) return rc;
+    if (n_proj < 1 || n_proj > kMaxProj || max_tokens < 1) return B200_LORA_ERR_DIM;
+    if (io_dtype != B200_LORA_F16 && io_dtype != B200_LORA_BF16) return B200_LORA_ERR_DTYPE;
+    if (y_dtype != io_dtype && y_dtype != B200_LORA_F32) return B200_LORA_ERR_DTYPE;
+    if (layer < 0 || layer >= adapters->n_layers) return B200_LORA_ERR_LAYER;
+    if (!aligned16(plan) || !aligned16(workspace)) return B200_LORA_ERR_ALIGN;
+
+    ApplyParams p;
+    memset(&p, 0, sizeof(p));
+    int max_h_in = 0;
+    for (int i = 0; i < n_proj; ++i) {
+        const b200_lora_proj& q = projs[i];
+        if (!q.x || !q.y || !q.wa || !q.wb) return B200_LORA_ERR_NULL;
+        if (q.h_in < 8 || q.h_out < 8 || (q.h_in % 8) || (q.h_out % 8)) return B200_LORA_ERR_DIM;
+        if (q.ldx < q.h_in || q.ldy < q.h_out || (q.ldx % 8) || (q.ldy % 8)) return B200_LORA_ERR_DIM;
+        if (!aligned16(q.x) || !aligned16(q.y) || !aligned16(q.wa) || !aligned16(q.wb)) return B200_LORA_ERR_ALIGN;
+        ProjArgs& a = p.proj[i];
+        a.x = q.x; a.y = q.y; a.wa = q.wa; a.wb = q.wb;
+        a.ldx = q.ldx; a.ldy = q.ldy; a.h_in = q.h_in; a.h_out = q.h_out;
+        a.n_super_in = (q.h_in + kSuper - 1) / kSuper;
+        a.n_super_out = (q.h_out + kSuper - 1) / kSuper;
+        p.total_super_in += a.n_super_in;
+        p.total_super_out += a.n_super_out;
+        if (q.h_in > max_h_in) max_h_in = q.h_in;
+    }
+    if (workspace_bytes_ < workspace_bytes(max_tokens, n_proj, max_h_in)) return B200_LORA_ERR_WORKSPACE;
+    p.n_proj = n_proj;
+    p.ranks = adapters->ranks;
+    p.scalings = adapters->scalings;
+    p.cum_ranks = reinterpret_cast<const long long*>(adapters->cum_ranks);
+    p.n_adapters = adapters->n_adapters;
+    p.n_layers = adapters->n_layers;
+    p.r_pool = adapters->r_pool;
+    p.packed = adapters->packed;
+    p.scale = adapters->scale;
+    p.layer = layer;
+    p.flags = flags;
+    p.y_f32 = (y_dtype == B200_LORA_F32);
+    p.cap = max_tokens;
+    p.plan = const_cast<void*>(plan);
+    p.workspace = workspace;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int n_sm = sm_count();
+    cudaError_t e = cudaSuccess;
+    if (!sgmv_tiles_supported(p)) p.flags |= B200_LORA_NO_TENSOR;
+    if (!(p.flags & B200_LORA_NO_TENSOR)) e = launch_sgmv_tiles(p, io_dtype, n_sm, s);
+    if (e == cudaSuccess) e = launch_bgmv(p, io_dtype, n_sm, s);
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+size_t b200_add_lora_bgmv_workspace_bytes(int32_t n_tokens, int32_t n_adapters, int32_t h_in) {
+    size_t pb = b200_lora_plan_bytes(n_tokens, n_adapters);
+    size_t wb = b200_lora_workspace_bytes(n_tokens, 1, h_in);
+    if (!pb || !wb) return 0;
+    return ((pb + 255) & ~size_t(255)) + wb;
+}
+
+int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void* wb_T_all,
+                       const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
+                       int32_t h_in, int32_t h_out, int32_t n_adapters, int32_t n_layers, int32_t r,
+                       int32_t layer_idx, float scale, int32_t dtype,
+                       void* workspace, size_t workspace_bytes_, void* stream) {
+    if (!workspace) return B200_LORA_ERR_NULL;
+    if (n_tokens < 1 || n_adapters < 1) return B200_LORA_ERR_DIM;
+    if (workspace_bytes_ < b200_add_lora_bgmv_workspace_bytes(n_tokens, n_adapters, h_in)) return B200_LORA_ERR_WORKSPACE;
+    b200_lora_adapters ad;
+    memset(&ad, 0, sizeof(ad));
+    ad.n_adapters = n_adapters; ad.n_layers = n_layers; ad.r_pool = r; ad.packed = 0; ad.scale = scale;
+    size_t pb = (b200_lora_plan_bytes(n_tokens, n_adapters) + 255) & ~size_t(255);
+    char* ws = static_cast<char*>(workspace) + pb;
+    int rc = b200_lora_plan_build(workspace, pb, n_tokens, indicies, indicies_are_i64, n_tokens, &ad, stream);
+    if (rc) return rc;
+    b200_lora_proj pj;
+    pj.x = x; pj.y = y; pj.wa = wa_T_all; pj.wb = wb_T_all;
+    pj.ldx = h_in; pj.ldy = h_out; pj.h_in = h_in; pj.h_out = h_out;
+    return b200_lora_apply(&pj, 1, &ad, workspace, n_tokens, layer_idx, dtype, dtype, 0, ws,
+                           workspace_bytes_ - pb, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,196 @@
+// Shared device/host definitions of the multi-LoRA delta kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "b200_lora.h"
+
+namespace b200lora {
+
+constexpr int kMaxRank = B200_LORA_MAX_RANK;   // 64
+constexpr int kMaxProj = B200_LORA_MAX_PROJ;   // 4
+constexpr int kSuper = 2048;                   // columns (shrink) / rows (expand) per super-chunk
+constexpr int kCtaThreads = 256;
+constexpr int kSlots = 8;                      // 128-bit loads each thread keeps in flight
+constexpr int kTokTile = 4;                    // tokens per register pass
+constexpr int kTallMin = 32;                   // a contiguous segment at least this long is "tall"
+constexpr int kTileM = 128;                    // token rows of one tensor-core tile
+
+// ---- plan layout --------------------------------------------------------------------------
+// All fields are int32.  `cap` is the token capacity the buffer was sized for.
+struct PlanHeader {
+    int n_tokens;
+    int n_segs;
+    int n_units;      // sum over short segments of r_pad/8
+    int error;        // 0 ok, 1 adapter id out of range, 2 bad segment table
+    int n_tiles;      // 128-row tiles of tall segments
+    int cap;
+    int n_adapters;
+    int identity;     // 1: perm is the identity (rows pre-grouped)
+    int n_units_short;  // units of short segments; they come first in unit_tab
+    int pad[7];
+};
+static_assert(sizeof(PlanHeader) == 64, "plan header is 16 words");
+
+struct PlanView {
+    PlanHeader* hdr;
+    int* perm;          // [cap]       sorted position -> token row
+    int* seg_start;     // [cap + 1]   sorted position of each segment's first token
+    int* seg_adapter;   // [cap]
+    int* seg_rank;      // [cap]       rank of the segment's adapter
+    int* seg_flags;     // [cap]       bit0: tall (handled by the tensor-core tiles)
+    int* unit_tab;      // [8 * cap]   (seg << 3) | sub
+    int* tile_tab;      // [cap]       (seg << 12) | m-tile, for tall segments (cap/kTallMin used)
+    int* hist;          // [n_adapters + 1]
+};
+
+__host__ __device__ inline size_t plan_words(int cap, int n_adapters) {
+    // header + perm + seg_start + 3 seg arrays + units + tiles + hist, each padded to 4 words
+    auto pad4 = [](size_t w) { return (w + 3) & ~size_t(3); };
+    return 16 + pad4(cap) + pad4(cap + 1) + 3 * pad4(cap) + pad4(8 * (size_t)cap) + pad4(cap) +
+           pad4((size_t)n_adapters + 1);
+}
+
+__host__ __device__ inline PlanView plan_view(void* base, int cap, int n_adapters) {
+    auto pad4 = [](size_t w) { return (w + 3) & ~size_t(3); };
+    int* w = reinterpret_cast<int*>(base);
+    PlanView v;
+    v.hdr = reinterpret_cast<PlanHeader*>(w);      w += 16;
+    v.perm = w;                                    w += pad4(cap);
+    v.seg_start = w;                               w += pad4(cap + 1);
+    v.seg_adapter = w;                             w += pad4(cap);
+    v.seg_rank = w;                                w += pad4(cap);
+    v.seg_flags = w;                               w += pad4(cap);
+    v.unit_tab = w;                                w += pad4(8 * (size_t)cap);
+    v.tile_tab = w;                                w += pad4(cap);
+    v.hist = w;
+    (void)n_adapters;
+    return v;
+}
+
+// ---- workspace layout ----------------------------------------------------------------------
+// control words (zero at rest), then the reduced intermediate v [n_proj][cap][64] fp32, then
+// the split-K partials [n_kchunk][n_proj][cap][64] fp32.
+struct WorkspaceCtl {
+    unsigned ticket[2];       // dynamic work tickets: shrink, expand
+    unsigned done[2];         // CTAs that have drained their queue
+    unsigned error;           // sticky device-side error word
+    unsigned pad[11];
+};
+static_assert(sizeof(WorkspaceCtl) == 64, "control block is 16 words");
+
+__host__ __device__ inline int max_kchunks(int h_in) { return (h_in + 255) / 256; }
+
+__host__ __device__ inline size_t ws_counter_words(int cap) { return (size_t)kMaxProj * cap; }
+
+__host__ __device__ inline size_t workspace_bytes(int cap, int n_proj, int max_h_in) {
+    size_t ctl = sizeof(WorkspaceCtl) + 4 * ((ws_counter_words(cap) + 3) & ~size_t(3));
+    size_t v = (size_t)n_proj * cap * kMaxRank * 4;
+    size_t part = (size_t)max_kchunks(max_h_in) * n_proj * cap * kMaxRank * 4;
+    return ctl + v + part + 256;
+}
+
+struct WorkspaceView {
+    WorkspaceCtl* ctl;
+    unsigned* counters;   // [kMaxProj][cap]  arrivals per (projection, segment)
+    float* v;             // [n_proj][cap][64]
+    float* partial;       // [kchunk][n_proj][cap][64]
+};
+
+__host__ __device__ inline WorkspaceView workspace_view(void* base, int cap, int n_proj) {
+    char* p = reinterpret_cast<char*>(base);
+    WorkspaceView w;
+    w.ctl = reinterpret_cast<WorkspaceCtl*>(p);            p += sizeof(WorkspaceCtl);
+    w.counters = reinterpret_cast<unsigned*>(p);           p += 4 * ((ws_counter_words(cap) + 3) & ~size_t(3));
+    p = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(p) + 127) & ~uintptr_t(127));
+    w.v = reinterpret_cast<float*>(p);                     p += (size_t)n_proj * cap * kMaxRank * 4;
+    w.partial = reinterpret_cast<float*>(p);
+    return w;
+}
+
+// ---- kernel parameters ------------------------------------------------------------------------
+struct ProjArgs {
+    const void* x;
+    void* y;
+    const void* wa;
+    const void* wb;
+    long long ldx, ldy;
+    int h_in, h_out;
+    int n_super_in, n_super_out;
+};
+
+struct ApplyParams {
+    ProjArgs proj[kMaxProj];
+    int n_proj;
+    int total_super_in, total_super_out;
+    const int* ranks;
+    const float* scalings;
+    const long long* cum_ranks;
+    int n_adapters, n_layers, r_pool, packed;
+    float scale;
+    int layer;
+    int flags;
+    int y_f32;
+    int cap;
+    void* plan;
+    void* workspace;
+};
+
+// element offset of adapter a's A block [r, h] for `layer`, and its row count / row pitch
+__device__ __forceinline__ long long block_row0(const ApplyParams& p, int a, int r) {
+    if (p.packed) return (long long)p.n_layers * p.cum_ranks[a] + (long long)p.layer * r;
+    return ((long long)a * p.n_layers + p.layer) * p.r_pool;
+}
+__device__ __forceinline__ int b_pitch(const ApplyParams& p, int r) { return p.packed ? r : p.r_pool; }
+
+__device__ __forceinline__ int pad_rank(int r) { return r <= 8 ? 8 : r <= 16 ? 16 : r <= 32 ? 32 : 64; }
+
+// ---- 16-bit -> fp32 helpers ------------------------------------------------------------------
+template <typename T> struct Cvt;
+template <> struct Cvt<__half> {
+    static __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ unsigned pack2(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<unsigned*>(&h);
+    }
+    static __device__ __forceinline__ float round1(float a) { return __half2float(__float2half_rn(a)); }
+};
+template <> struct Cvt<__nv_bfloat16> {
+    static __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+        const unsigned* w = reinterpret_cast<const unsigned*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+    }
+    static __device__ __forceinline__ unsigned pack2(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<unsigned*>(&h);
+    }
+    static __device__ __forceinline__ float round1(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
+};
+
+__device__ __forceinline__ uint4 ldg_nc16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+// ---- launchers implemented by the kernel files ---------------------------------------------
+cudaError_t launch_plan_build(void* plan, int cap, const void* ids, int ids_i64, int n_tokens,
+                              const int* ranks, int r_pool, int n_adapters, cudaStream_t s);
+cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts, const int* seg_adapter,
+                                      int n_segs, int n_tokens, const int* ranks, int r_pool,
+                                      int n_adapters, cudaStream_t s);
+cudaError_t launch_bgmv(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
+bool sgmv_tiles_supported(const ApplyParams& p);
+cudaError_t launch_sgmv_tiles(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
+
+}  // namespace b200lora

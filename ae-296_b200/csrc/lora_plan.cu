@@ -1,0 +1,224 @@
+// Plan build: adapter-index gather and segment bookkeeping on the device.
+//
+// One CTA turns the per-token adapter ids into
+//   perm         stable counting sort (token order kept inside one adapter)
+//   seg_*        one segment per adapter that has tokens, ascending adapter id
+//   unit_tab     the 32 KB weight units the BGMV kernels walk: short segments first
+//   tile_tab     128-row tiles of tall contiguous segments for the tensor-core kernel
+// It replaces the reference's precomputed index tensor (lightllm/models/lora_gpu.py:120,124)
+// and is integer work only: the tests require it bit-exact against a stable argsort.
+#include "lora_common.cuh"
+
+namespace b200lora {
+
+constexpr int kPlanThreads = 1024;
+
+// exclusive scan of one int per thread over the CTA; returns the prefix, `total` the CTA sum
+__device__ int block_scan_excl(int val, int& total, int* warp_sums) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int inc = val;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
+    }
+    __syncthreads();                       // warp_sums may still be read from a previous call
+    if (lane == 31) warp_sums[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        int w = warp_sums[lane];
+        int winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += n;
+        }
+        warp_sums[lane] = winc - w;        // exclusive prefix of warp totals
+        if (lane == 31) warp_sums[32] = winc;
+    }
+    __syncthreads();
+    total = warp_sums[32];
+    return warp_sums[wid] + inc - val;
+}
+
+template <typename IdT>
+__device__ __forceinline__ int load_id(const void* ids, int t) {
+    return (int)reinterpret_cast<const IdT*>(ids)[t];
+}
+
+// Phase A (ids known): histogram, segment table, stable placement.
+template <typename IdT>
+__device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* smem) {
+    const int tid = threadIdx.x;
+    int* warp_sums = smem;              // 33 words
+    int* s_bad = smem + 40;
+    if (tid == 0) *s_bad = 0;
+    for (int a = tid; a <= N; a += kPlanThreads) pv.hist[a] = 0;
+    __syncthreads();
+    for (int t = tid; t < T; t += kPlanThreads) {
+        int a = load_id<IdT>(ids, t);
+        if (a < 0 || a >= N) *s_bad = 1;
+        else atomicAdd(&pv.hist[a], 1);
+    }
+    __syncthreads();
+    if (*s_bad) {                        // leave an empty plan that applies nothing
+        if (tid == 0) { pv.hdr->error = 1; pv.hdr->n_segs = 0; pv.hdr->n_tokens = 0; }
+        return;
+    }
+    // exclusive scan over adapters: token offset and segment index
+    int tok_carry = 0, seg_carry = 0;
+    for (int base = 0; base < N; base += kPlanThreads) {
+        int a = base + tid;
+        int c = a < N ? pv.hist[a] : 0;
+        int tot_c, tot_s;
+        int off = block_scan_excl(c, tot_c, warp_sums);
+        int sidx = block_scan_excl(c > 0 ? 1 : 0, tot_s, warp_sums);
+        if (a < N) {
+            if (c > 0) {
+                pv.seg_start[seg_carry + sidx] = tok_carry + off;
+                pv.seg_adapter[seg_carry + sidx] = a;
+            }
+            pv.hist[a] = tok_carry + off;   // becomes the placement cursor
+        }
+        tok_carry += tot_c;
+        seg_carry += tot_s;
+    }
+    if (tid == 0) { pv.seg_start[seg_carry] = T; pv.hdr->n_segs = seg_carry; pv.hdr->n_tokens = T; }
+    __syncthreads();
+    // stable placement, one CTA-wide tile of tokens at a time, warps in order
+    const int lane = tid & 31, wid = tid >> 5;
+    for (int base = 0; base < T; base += kPlanThreads) {
+        int t = base + tid;
+        bool valid = t < T;
+        int a = valid ? load_id<IdT>(ids, t) : -1 - lane;      // distinct dummies never match
+        unsigned peers = __match_any_sync(0xffffffffu, a);
+        int rank_in_warp = __popc(peers & ((1u << lane) - 1));
+        int leader = __ffs(peers) - 1;
+        int cnt = __popc(peers);
+        int n_warps = min(kPlanThreads / 32, (T - base + 31) / 32);
+        int slot = 0;
+        for (int w = 0; w < n_warps; ++w) {
+            if (wid == w && valid && lane == leader) {
+                slot = pv.hist[a];
+                pv.hist[a] = slot + cnt;
+            }
+            __syncthreads();
+        }
+        slot = __shfl_sync(0xffffffffu, slot, leader);
+        if (valid) pv.perm[slot + rank_in_warp] = t;
+    }
+    __syncthreads();
+}
+
+// Phase B: classify segments, lay out units and tiles.
+__device__ void build_units(PlanView pv, const int* ranks, int r_pool, int* smem) {
+    const int tid = threadIdx.x;
+    int* warp_sums = smem;
+    const int S = pv.hdr->n_segs;
+    const bool identity = pv.hdr->identity != 0;
+    // pass 1: rank, tall flag; count units of short and of tall segments, and tiles
+    int tot_short = 0, tot_tall = 0, tot_tiles = 0;
+    for (int pass = 0; pass < 2; ++pass) {
+        int c_short = 0, c_tall = 0, c_tiles = 0;
+        for (int base = 0; base < S; base += kPlanThreads) {
+            int s = base + tid;
+            int us = 0, ut = 0, nt = 0, r = 0, tall = 0, len = 0;
+            if (s < S) {
+                int a = pv.seg_adapter[s];
+                r = ranks ? ranks[a] : r_pool;
+                if (r < 1) r = 1;
+                if (r > kMaxRank) r = kMaxRank;
+                int b = pv.seg_start[s], e = pv.seg_start[s + 1];
+                len = e - b;
+                bool contig = identity || (pv.perm[e - 1] - pv.perm[b] == len - 1);
+                tall = (len >= kTallMin && contig) ? 1 : 0;
+                int u = pad_rank(r) / 8;
+                us = tall ? 0 : u;
+                ut = tall ? u : 0;
+                nt = tall ? (len + kTileM - 1) / kTileM : 0;
+            }
+            int t0, t1, t2;
+            int o_s = block_scan_excl(us, t0, warp_sums);
+            int o_t = block_scan_excl(ut, t1, warp_sums);
+            int o_m = block_scan_excl(nt, t2, warp_sums);
+            if (pass == 1 && s < S) {
+                pv.seg_rank[s] = r;
+                pv.seg_flags[s] = tall;
+                int u0 = tall ? tot_short + c_tall + o_t : c_short + o_s;
+                for (int j = 0; j < us + ut; ++j) pv.unit_tab[u0 + j] = (s << 3) | j;
+                for (int m = 0; m < nt; ++m) pv.tile_tab[c_tiles + o_m + m] = (s << 12) | m;
+            }
+            c_short += t0; c_tall += t1; c_tiles += t2;
+        }
+        tot_short = c_short; tot_tall = c_tall; tot_tiles = c_tiles;
+    }
+    if (tid == 0) {
+        pv.hdr->n_units = tot_short + tot_tall;
+        pv.hdr->n_units_short = tot_short;
+        pv.hdr->n_tiles = tot_tiles;
+    }
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kPlanThreads, 1)
+plan_build_kernel(void* plan, int cap, const void* ids, int T, const int* ranks, int r_pool, int N) {
+    __shared__ int smem[64];
+    PlanView pv = plan_view(plan, cap, N);
+    if (threadIdx.x == 0) {
+        pv.hdr->error = 0; pv.hdr->cap = cap; pv.hdr->n_adapters = N; pv.hdr->identity = 0;
+        pv.hdr->n_units = 0; pv.hdr->n_tiles = 0; pv.hdr->n_units_short = 0; pv.hdr->n_segs = 0; pv.hdr->n_tokens = 0;
+    }
+    __syncthreads();
+    build_from_ids<IdT>(pv, ids, T, N, smem);
+    __syncthreads();
+    if (pv.hdr->error) return;
+    build_units(pv, ranks, r_pool, smem);
+}
+
+__global__ void __launch_bounds__(kPlanThreads, 1)
+plan_segments_kernel(void* plan, int cap, const int* seg_starts, const int* seg_adapter, int S, int T,
+                     const int* ranks, int r_pool, int N) {
+    __shared__ int smem[64];
+    PlanView pv = plan_view(plan, cap, N);
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        pv.hdr->error = 0; pv.hdr->cap = cap; pv.hdr->n_adapters = N; pv.hdr->identity = 1;
+        pv.hdr->n_units = 0; pv.hdr->n_tiles = 0; pv.hdr->n_units_short = 0; pv.hdr->n_segs = 0; pv.hdr->n_tokens = 0;
+        smem[40] = 0;
+    }
+    __syncthreads();
+    // validate: offsets start at 0, end at T, strictly increase; adapters in range
+    for (int s = tid; s < S; s += kPlanThreads) {
+        int b = seg_starts[s], e = seg_starts[s + 1], a = seg_adapter[s];
+        if (b < 0 || e <= b || e > T) smem[40] = 2;
+        if (a < 0 || a >= N) smem[40] = 1;
+        if (s == 0 && b != 0) smem[40] = 2;
+        if (s == S - 1 && e != T) smem[40] = 2;
+    }
+    __syncthreads();
+    if (smem[40]) { if (tid == 0) pv.hdr->error = smem[40]; return; }
+    for (int s = tid; s < S; s += kPlanThreads) { pv.seg_start[s] = seg_starts[s]; pv.seg_adapter[s] = seg_adapter[s]; }
+    for (int t = tid; t < T; t += kPlanThreads) pv.perm[t] = t;
+    if (tid == 0) { pv.seg_start[S] = T; pv.hdr->n_segs = S; pv.hdr->n_tokens = T; }
+    __syncthreads();
+    build_units(pv, ranks, r_pool, smem);
+}
+
+cudaError_t launch_plan_build(void* plan, int cap, const void* ids, int ids_i64, int n_tokens,
+                              const int* ranks, int r_pool, int n_adapters, cudaStream_t s) {
+    if (ids_i64)
+        plan_build_kernel<long long><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ranks, r_pool, n_adapters);
+    else
+        plan_build_kernel<int><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ranks, r_pool, n_adapters);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts, const int* seg_adapter,
+                                      int n_segs, int n_tokens, const int* ranks, int r_pool,
+                                      int n_adapters, cudaStream_t s) {
+    plan_segments_kernel<<<1, kPlanThreads, 0, s>>>(plan, cap, seg_starts, seg_adapter, n_segs, n_tokens,
+                                                    ranks, r_pool, n_adapters);
+    return cudaGetLastError();
+}
+
+}  // namespace b200lora

@@ -1,0 +1,220 @@
+"""Python-facing multi-LoRA ops: thin wrappers that pass tensor addresses to the C ABI.
+
+``add_lora_bgmv`` keeps the positional signature the reference's layer code calls
+(``punica.ops.add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx, scale)``,
+lightllm/models/lora_gpu.py:138,150,162).  The generalised ops add per-adapter ranks and
+scalings, packed pools, adapter-sorted segments and fused q/k/v application.
+
+PyTorch is used for device memory and streams only; all arithmetic runs in the CUDA
+library, and there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import Adapters, LoraError, Proj, check
+from .pool import AdapterPool
+
+_DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise ValueError("LoRA ops need CUDA tensors (no CPU path exists)")
+
+
+def _adapters_struct(n_adapters, n_layers, r_pool, ranks=None, scalings=None, cum_ranks=None,
+                     packed=False, scale=1.0) -> Adapters:
+    return Adapters(
+        ranks.data_ptr() if ranks is not None else None,
+        scalings.data_ptr() if scalings is not None else None,
+        cum_ranks.data_ptr() if cum_ranks is not None else None,
+        n_adapters, n_layers, r_pool, 1 if packed else 0, float(scale))
+
+
+def adapters_of(pool: AdapterPool) -> Adapters:
+    return _adapters_struct(pool.n_adapters, pool.n_layers, pool.r_pool, pool.ranks, pool.scalings,
+                            pool.cum_ranks, pool.packed, 1.0)
+
+
+class LoraPlan:
+    """Device-resident segment table of one batch (see ``b200_lora_plan_build``)."""
+
+    def __init__(self, max_tokens: int, n_adapters: int, device="cuda"):
+        self.max_tokens, self.n_adapters = int(max_tokens), int(n_adapters)
+        nbytes = _lib.lib().b200_lora_plan_bytes(self.max_tokens, self.n_adapters)
+        if nbytes == 0:
+            raise ValueError("bad plan dimensions")
+        self.buf = torch.zeros((nbytes + 15) // 16 * 2, dtype=torch.int64, device=device)
+        self.nbytes = self.buf.numel() * 8
+        self._keep = None
+
+    def build(self, ids: torch.Tensor, adapters: Adapters) -> "LoraPlan":
+        _require_cuda(ids)
+        if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
+            raise ValueError("ids must be a contiguous int32/int64 tensor")
+        check(_lib.lib().b200_lora_plan_build(
+            self.buf.data_ptr(), self.nbytes, self.max_tokens, ids.data_ptr(),
+            1 if ids.dtype == torch.int64 else 0, ids.numel(), C.byref(adapters), _stream(ids.device)),
+            "plan_build")
+        return self
+
+    def from_segments(self, seg_starts: torch.Tensor, seg_adapter: torch.Tensor, n_tokens: int,
+                      adapters: Adapters) -> "LoraPlan":
+        _require_cuda(seg_starts, seg_adapter)
+        if seg_starts.dtype != torch.int32 or seg_adapter.dtype != torch.int32:
+            raise ValueError("segment tables must be int32")
+        self._keep = (seg_starts, seg_adapter)
+        check(_lib.lib().b200_lora_plan_from_segments(
+            self.buf.data_ptr(), self.nbytes, self.max_tokens, seg_starts.data_ptr(), seg_adapter.data_ptr(),
+            seg_adapter.numel(), int(n_tokens), C.byref(adapters), _stream(seg_starts.device)),
+            "plan_from_segments")
+        return self
+
+    def read(self) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+        """(perm, seg_starts, seg_adapter) as host arrays; raises on a bad id or segment table."""
+        perm = np.zeros(self.max_tokens, np.int32)
+        starts = np.zeros(self.max_tokens + 1, np.int32)
+        adapter = np.zeros(self.max_tokens, np.int32)
+        ns, nt = C.c_int32(0), C.c_int32(0)
+        check(_lib.lib().b200_lora_plan_read(
+            self.buf.data_ptr(), perm.ctypes.data, starts.ctypes.data, adapter.ctypes.data,
+            C.byref(ns), C.byref(nt), _stream(self.buf.device)), "plan_read")
+        return perm[:nt.value], starts[:ns.value + 1], adapter[:ns.value]
+
+
+class LoraWorkspace:
+    """Scratch for the ``[T, r]`` intermediate and the split-K partial sums."""
+
+    def __init__(self, max_tokens: int, n_proj: int, max_h_in: int, device="cuda"):
+        self.max_tokens, self.n_proj, self.max_h_in = int(max_tokens), int(n_proj), int(max_h_in)
+        nbytes = _lib.lib().b200_lora_workspace_bytes(self.max_tokens, self.n_proj, self.max_h_in)
+        if nbytes == 0:
+            raise ValueError("bad workspace dimensions")
+        self.buf = torch.zeros((nbytes + 15) // 16 * 2, dtype=torch.int64, device=device)   # zero-filled once
+        self.nbytes = self.buf.numel() * 8
+
+
+def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan: LoraPlan, layer: int,
+          workspace: LoraWorkspace, flags: int = 0, adapters: Optional[Adapters] = None) -> None:
+    """``y += scale_a * (x @ A_a^T) @ B_a^T`` for up to four projections ``(x, y, pool)`` of one layer.
+
+    All pools must share one adapter table (ranks, scalings, layout)."""
+    if not 1 <= len(projs) <= _lib.MAX_PROJ:
+        raise ValueError("1..4 projections per call")
+    arr = (Proj * len(projs))()
+    io = None
+    ydt = None
+    for i, (x, y, pool) in enumerate(projs):
+        _require_cuda(x, y, pool.wa)
+        if x.dim() != 2 or y.dim() != 2 or x.shape[0] != y.shape[0]:
+            raise ValueError("x and y must be [T, h] with the same T")
+        if x.stride(1) != 1 or y.stride(1) != 1:
+            raise ValueError("x and y rows must be contiguous")
+        if x.shape[1] != pool.h_in or y.shape[1] != pool.h_out:
+            raise ValueError("x/y widths do not match the pool")
+        if x.dtype != pool.wa.dtype or x.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("x and the pool must both be fp16 or both bf16")
+        if io is None:
+            io, ydt = x.dtype, y.dtype
+        if x.dtype != io or y.dtype != ydt or ydt not in (io, torch.float32):
+            raise ValueError("all projections share the I/O dtype; y is that dtype or fp32")
+        if x.shape[0] > plan.max_tokens:
+            raise ValueError("more tokens than the plan was sized for")
+        arr[i] = Proj(x.data_ptr(), y.data_ptr(), pool.wa.data_ptr(), pool.wb.data_ptr(),
+                      x.stride(0), y.stride(0), pool.h_in, pool.h_out)
+    ad = adapters if adapters is not None else adapters_of(projs[0][2])
+    check(_lib.lib().b200_lora_apply(
+        arr, len(projs), C.byref(ad), plan.buf.data_ptr(), plan.max_tokens, int(layer), _DT[io], _DT[ydt],
+        int(flags), workspace.buf.data_ptr(), workspace.nbytes, _stream(projs[0][0].device)), "apply")
+
+
+# ---- cached scratch for the one-call ops -------------------------------------------------------
+_SCRATCH = {}
+
+
+def _scratch(device, nbytes: int) -> torch.Tensor:
+    key = (torch.device(device).index, _stream(device))
+    buf = _SCRATCH.get(key)
+    if buf is None or buf.numel() * 8 < nbytes:
+        buf = torch.zeros((nbytes + 15) // 16 * 2, dtype=torch.int64, device=device)
+        _SCRATCH[key] = buf
+    return buf
+
+
+def add_lora_bgmv(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T_all: torch.Tensor,
+                  indicies: torch.Tensor, layer_idx: int, scale: float) -> None:
+    """In place ``y[t] += scale * (x[t] @ wa_T_all[i_t, layer]^T) @ wb_T_all[i_t, layer]^T``.
+
+    Same arguments as the reference's decode op: ``y [T, h_out]``, ``x [T, h_in]``,
+    ``wa_T_all [N, L, r, h_in]``, ``wb_T_all [N, L, h_out, r]`` contiguous fp16/bf16 CUDA
+    tensors, ``indicies [T]`` int64 (or int32) CUDA tensor.  Returns ``None``.
+    """
+    _require_cuda(y, x, wa_T_all, wb_T_all, indicies)
+    if wa_T_all.dim() != 4 or wb_T_all.dim() != 4:
+        raise ValueError("weight pools must be [N, L, r, h_in] and [N, L, h_out, r]")
+    n, l, r, h_in = wa_T_all.shape
+    h_out = wb_T_all.shape[2]
+    if tuple(wb_T_all.shape) != (n, l, h_out, r):
+        raise ValueError("wa_T_all / wb_T_all shapes disagree")
+    t = x.shape[0]
+    if tuple(x.shape) != (t, h_in) or tuple(y.shape) != (t, h_out) or indicies.numel() != t:
+        raise ValueError("x, y, indicies shapes disagree with the pools")
+    for ten in (y, x, wa_T_all, wb_T_all, indicies):
+        if not ten.is_contiguous():
+            raise ValueError("add_lora_bgmv needs contiguous tensors")
+    if not (y.dtype == x.dtype == wa_T_all.dtype == wb_T_all.dtype) or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("fp16 or bf16 tensors of one dtype expected")
+    if indicies.dtype not in (torch.int32, torch.int64):
+        raise ValueError("indicies must be int32 or int64")
+    L = _lib.lib()
+    nbytes = L.b200_add_lora_bgmv_workspace_bytes(t, n, h_in)
+    if nbytes == 0:
+        raise ValueError("bad dimensions")
+    ws = _scratch(x.device, nbytes)
+    check(L.b200_add_lora_bgmv(
+        y.data_ptr(), x.data_ptr(), wa_T_all.data_ptr(), wb_T_all.data_ptr(), indicies.data_ptr(),
+        1 if indicies.dtype == torch.int64 else 0, t, h_in, h_out, n, l, r, int(layer_idx), float(scale),
+        _DT[x.dtype], ws.data_ptr(), ws.numel() * 8, _stream(x.device)), "add_lora_bgmv")
+
+
+class LoraBatch:
+    """Plan + workspace of one batch, reused across layers and projections."""
+
+    def __init__(self, max_tokens: int, n_adapters: int, max_h_in: int, n_proj: int = 4, device="cuda"):
+        self.plan = LoraPlan(max_tokens, n_adapters, device)
+        self.workspace = LoraWorkspace(max_tokens, n_proj, max_h_in, device)
+
+    def set_ids(self, ids: torch.Tensor, pool: AdapterPool) -> "LoraBatch":
+        self.plan.build(ids, adapters_of(pool))
+        return self
+
+    def set_segments(self, seg_starts, seg_adapter, n_tokens, pool: AdapterPool) -> "LoraBatch":
+        self.plan.from_segments(seg_starts, seg_adapter, n_tokens, adapters_of(pool))
+        return self
+
+    def apply(self, projs, layer: int, flags: int = 0) -> None:
+        apply(projs, self.plan, layer, self.workspace, flags)
+
+
+def add_lora_bgmv_v2(y, x, pool: AdapterPool, indicies, layer_idx: int, flags: int = 0) -> None:
+    """BGMV with per-adapter ranks and scalings taken from ``pool`` (dense or packed)."""
+    b = LoraBatch(x.shape[0], pool.n_adapters, pool.h_in, 1, x.device).set_ids(indicies, pool)
+    b.apply([(x, y, pool)], layer_idx, flags)
+
+
+def add_lora_sgmv(y, x, pool: AdapterPool, seg_starts, seg_adapter, layer_idx: int, flags: int = 0) -> None:
+    """SGMV on adapter-sorted rows: segment ``s`` = rows ``[seg_starts[s], seg_starts[s+1])``."""
+    b = LoraBatch(x.shape[0], pool.n_adapters, pool.h_in, 1, x.device)
+    b.set_segments(seg_starts, seg_adapter, x.shape[0], pool)
+    b.apply([(x, y, pool)], layer_idx, flags)

@@ -1,0 +1,301 @@
+"""Benchmark of the multi-LoRA delta path: one step = one full-model pass (every layer, q/k/v/o).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM (CUDA-graph
+replay of the whole pass, CUDA-event timed, max over ranks); `e2e` is the same pass driven
+from pinned host buffers through the public ops, host<->device copies inside the timed
+region; `roofline` is the expand kernel (the larger half of the traffic) timed alone;
+`cpu_baseline` is the reference's CPU LoRA arithmetic timed on this host's cores.
+With N > 1 each rank holds its own adapters and batch (placement by adapter, no collective).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", type=int, default=1)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="override depth (0 = the workload's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args, rank, world):
+    """The reference's CPU LoRA arithmetic on this host's cores (oracle port), all cores."""
+    if rank != 0:
+        return
+    from ae296_b200.workloads import make_workload
+    from oracle.cpu_baseline import time_cpu_lora
+    wl = make_workload(args.workload)
+    res = time_cpu_lora(wl, sample_layers=1, reps=max(2, args.steps // 4 + 1))
+    out = {
+        "impl": "reference", "metric": "lora_shrink_expand_tokens_per_s", "value": res["tokens_per_s"],
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": res["seconds_per_layer"] * wl.n_layers * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"cfg{wl.cfg}:{wl.name}", "tokens": wl.n_tokens, "layers": wl.n_layers},
+        "cpu_baseline": {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"],
+                         "kind": "port", "sample": res["sample"]},
+        "e2e": {"value": res["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import ae296_b200 as L
+    from ae296_b200 import _lib
+    from ae296_b200.workloads import make_workload, materialize_device
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = make_workload(args.workload)
+    n_layers = args.layers or wl.n_layers
+    # keep the resident pool within one GPU: trim depth if the full pool would not fit
+    free_b, _ = torch.cuda.mem_get_info()
+    per_layer_pool = wl.pool_bytes() // wl.n_layers
+    fit_layers = int((free_b * 0.8) // (per_layer_pool + 1))
+    depth_note = None
+    if n_layers > fit_layers:
+        depth_note = f"pool trimmed to {fit_layers} of {n_layers} layers to fit one GPU"
+        n_layers = fit_layers
+    T = wl.n_tokens
+    x_qkv, x_o, pools = materialize_device(wl, dev, layers=n_layers)
+    dt = x_qkv.dtype
+    names = [p.name for p in wl.projections]
+    ys = {p.name: torch.zeros(n_layers, T, p.h_out, dtype=dt, device=dev) for p in wl.projections}
+    ids_host = torch.from_numpy(wl.ids).pin_memory()
+    ids = ids_host.to(dev)
+    batch = L.LoraBatch(T, wl.n_adapters, wl.projections[0].h_in, 3, dev)
+    stream = torch.cuda.Stream(dev)
+
+    def one_pass(flags=0):
+        batch.set_ids(ids, pools["q"])
+        for l in range(n_layers):
+            batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l, flags)
+            batch.apply([(x_o[l], ys["o"][l], pools["o"])], l, flags)
+
+    launches_per_pass = 1 + n_layers * 4
+
+    def capture(flags=0):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            one_pass(flags)
+            stream.synchronize()
+            with torch.cuda.graph(g, stream=stream):
+                one_pass(flags)
+        return g
+
+    def timed(graph, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                graph.replay()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        return e0.elapsed_time(e1) / steps       # ms per step
+
+    g_full = capture(0)
+    with ClockSampler(local) as clk:
+        ms = timed(g_full, args.steps, max(args.warmup, 3))
+    if world > 1:
+        tms = torch.tensor([ms], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+
+    # roofline of the dominant kernel (expand) and of the shrink, each timed alone
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    used = wl.distinct()
+    rsum = int(wl.ranks[used].sum())
+    e = 2
+    exp_bytes = sum(rsum * p.h_out * e + 2 * T * p.h_out * e for p in wl.projections) * n_layers
+    shr_bytes = sum(rsum * p.h_in * e + T * p.h_in * e + 4 * T for p in wl.projections) * n_layers
+    ms_exp = timed(capture(_lib.ONLY_EXPAND), args.steps, 3)
+    ms_shr = timed(capture(_lib.ONLY_SHRINK), args.steps, 3)
+    n_exp_launch = n_layers * 2
+    ach = exp_bytes / (ms_exp * 1e-3) / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "bgmv_expand_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
+        "frac": ach / peak, "traffic": None, "peak_source": peak_src,
+        "bytes_per_launch": exp_bytes / n_exp_launch, "us_per_launch": ms_exp * 1e3 / n_exp_launch,
+        "frac_of_8TBs_nominal": ach / 8000.0,
+        "shrink": {"kernel": "bgmv_shrink_kernel", "achieved": shr_bytes / (ms_shr * 1e-3) / 1e9,
+                   "frac": shr_bytes / (ms_shr * 1e-3) / 1e9 / peak, "us_per_launch": ms_shr * 1e3 / n_exp_launch},
+        "whole_pass": {"bytes": wl.bytes_per_layer() * n_layers,
+                       "achieved": wl.bytes_per_layer() * n_layers / (ms * 1e-3) / 1e9,
+                       "frac": wl.bytes_per_layer() * n_layers / (ms * 1e-3) / 1e9 / peak},
+    }
+
+    # end to end from pinned host buffers through the public ops
+    e2e = None
+    if not args.no_e2e:
+        hx_qkv = torch.empty(x_qkv.shape, dtype=dt).pin_memory().copy_(x_qkv.cpu())
+        hx_o = torch.empty(x_o.shape, dtype=dt).pin_memory().copy_(x_o.cpu())
+        hy = {n: torch.empty(ys[n].shape, dtype=dt).pin_memory() for n in names}
+        copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+        def e2e_step():
+            with torch.cuda.stream(stream):
+                ids.copy_(ids_host, non_blocking=True)
+                batch.set_ids(ids, pools["q"])
+            ev_in, ev_done = [], []
+            with torch.cuda.stream(copy_in):
+                for l in range(n_layers):
+                    x_qkv[l].copy_(hx_qkv[l], non_blocking=True)
+                    x_o[l].copy_(hx_o[l], non_blocking=True)
+                    ev = torch.cuda.Event(); ev.record(copy_in); ev_in.append(ev)
+            with torch.cuda.stream(stream):
+                for l in range(n_layers):
+                    stream.wait_event(ev_in[l])
+                    batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
+                    batch.apply([(x_o[l], ys["o"][l], pools["o"])], l)
+                    ev = torch.cuda.Event(); ev.record(stream); ev_done.append(ev)
+            with torch.cuda.stream(copy_out):
+                for l in range(n_layers):
+                    copy_out.wait_event(ev_done[l])
+                    for n in names:
+                        hy[n][l].copy_(ys[n][l], non_blocking=True)
+            stream.wait_stream(copy_out)
+
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        k = max(3, args.steps // 4)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(k):
+            e2e_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - t0) / k * 1e3
+        ms_e2e = max(e0.elapsed_time(e1) / k, wall)
+        if world > 1:
+            tms = torch.tensor([ms_e2e], device=dev)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            ms_e2e = float(tms.item())
+        h2d = (hx_qkv.numel() + hx_o.numel()) * 2 + ids_host.numel() * 4
+        d2h = sum(hy[n].numel() for n in names) * 2
+        e2e = {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle.cpu_baseline import time_cpu_lora
+        res = time_cpu_lora(wl, sample_layers=1, reps=4)
+        cpu = {"value": res["tokens_per_s"], "unit": "tokens/s", "cores": res["cores"], "kind": "port",
+               "sample": res["sample"]}
+
+    if rank == 0:
+        out = {
+            "metric": "lora_shrink_expand_tokens_per_s", "value": world * T / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32-accumulate/" + wl.dtype, "data": "synthetic",
+            "config": {"workload": f"cfg{wl.cfg}:{wl.name}", "tokens_per_gpu": T, "layers": n_layers,
+                       "adapters": wl.n_adapters, "distinct_adapters": int(len(used)), "projections": "q,k,v,o",
+                       "pool_gb": round(sum(p.nbytes() for p in pools.values()) / 1e9, 3),
+                       "l2": "inputs larger than L2 (per-step working set >> 126 MB)",
+                       "parallelism": "1 GPU" if world == 1 else f"{world} replicas placed by adapter, no collective",
+                       "note": depth_note},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": launches_per_pass * args.steps, "clocks": clk.summary(),
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

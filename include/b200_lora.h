@@ -1,0 +1,142 @@
+/*
+ * b200_lora.h - C ABI of the B200 (sm_100a) multi-LoRA delta library.
+ *
+ *     y[t, :] += scale_a * (x[t, :] . A_a^T) . B_a^T        a = adapter of token t
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" is a CUDA device
+ * address on the current device; the caller owns all memory.  No entry point
+ * allocates device memory (except where a comment says it owns a static
+ * array), synchronises the stream, or throws: each returns a b200_lora_status.
+ * All work is enqueued on the `stream` argument (a cudaStream_t passed as
+ * void*), so calls are stream-ordered and re-entrant across streams as long
+ * as plans and workspaces are not shared between streams.
+ *
+ * Weight layout (the reference's stacked pools, lightllm/models/lora_gpu.py:33-40):
+ *   dense  : wa [N, L, R, h_in]  (h_in contiguous),  wb [N, L, h_out, R] (R contiguous)
+ *   packed : adapter a owns rows [L*cum[a], L*cum[a+1]) of a [L*sum(r), h] matrix,
+ *            layer l at row L*cum[a] + l*r_a; wb's (a,l) block is a contiguous [h_out, r_a].
+ */
+#ifndef B200_LORA_H
+#define B200_LORA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200_lora_status {
+    B200_LORA_OK = 0,
+    B200_LORA_ERR_NULL = -1,       /* a required pointer is NULL */
+    B200_LORA_ERR_DIM = -2,        /* a dimension is zero, negative, or not a multiple of 8 */
+    B200_LORA_ERR_DTYPE = -3,      /* unsupported element type */
+    B200_LORA_ERR_ALIGN = -4,      /* a pointer or leading dimension is not 16-byte aligned */
+    B200_LORA_ERR_RANK = -5,       /* rank outside [1, B200_LORA_MAX_RANK] */
+    B200_LORA_ERR_WORKSPACE = -6,  /* plan or workspace buffer too small */
+    B200_LORA_ERR_CUDA = -7,       /* a CUDA runtime call failed; see b200_lora_last_cuda_error */
+    B200_LORA_ERR_ID_RANGE = -8,   /* plan build saw an adapter id outside [0, N) */
+    B200_LORA_ERR_LAYER = -9,      /* layer index outside [0, L) */
+    B200_LORA_ERR_SEGMENTS = -10,  /* segment offsets not monotone or not covering [0, T] */
+    B200_LORA_ERR_TIMEOUT = -11,   /* a bounded device-side wait expired */
+    B200_LORA_ERR_UNSUPPORTED = -12
+} b200_lora_status;
+
+enum { B200_LORA_F16 = 0, B200_LORA_BF16 = 1, B200_LORA_F32 = 2 };
+enum { B200_LORA_MAX_RANK = 64, B200_LORA_MAX_PROJ = 4 };
+
+/* flags of b200_lora_apply */
+enum {
+    B200_LORA_MID_ROUND = 1,   /* round the [T, r] intermediate to the I/O type, as the reference's
+                                  batched-matmul prefill op does (lightllm/models/lora_gpu.py:127-128) */
+    B200_LORA_NO_TENSOR = 2,   /* keep tall segments on the BGMV kernels too (no tcgen05 tiles) */
+    B200_LORA_ONLY_SHRINK = 4, /* profiling: run only the shrink half (v is left in the workspace) */
+    B200_LORA_ONLY_EXPAND = 8  /* profiling: run only the expand half on the workspace's current v */
+};
+
+/* The adapter table shared by the projections of one layer.
+ * Mirrors the pool attributes of Lora_GPU (lightllm/models/lora_gpu.py:24-40) and adds
+ * per-adapter ranks and scalings, which the reference fixes to one rank and scale 1. */
+typedef struct b200_lora_adapters {
+    const int32_t* ranks;      /* device [N]; NULL: every adapter has rank r_pool */
+    const float*   scalings;   /* device [N]; NULL: every adapter uses `scale` */
+    const int64_t* cum_ranks;  /* device [N+1] exclusive prefix of ranks; required when packed */
+    int32_t n_adapters;        /* N */
+    int32_t n_layers;          /* L */
+    int32_t r_pool;            /* R of the dense layout; upper bound of every rank */
+    int32_t packed;            /* 0 dense, 1 packed */
+    float   scale;
+} b200_lora_adapters;
+
+/* One projection (q, k, v or o): replaces one (x, pool pair, y) triple of
+ * Lora_GPU.invoke_one_layer_{q,k,v} (lightllm/models/lora_gpu.py:122-163). */
+typedef struct b200_lora_proj {
+    const void* x;   /* device [T, h_in], row stride ldx elements */
+    void*       y;   /* device [T, h_out], row stride ldy elements; accumulated in place */
+    const void* wa;  /* device A pool */
+    const void* wb;  /* device B pool */
+    int64_t ldx, ldy;
+    int32_t h_in, h_out;
+} b200_lora_proj;
+
+/* Library / build identification: returns the compiled-for architecture (100). */
+int b200_lora_arch(void);
+/* Text of the last CUDA error this thread's calls observed ("" if none). */
+const char* b200_lora_last_cuda_error(void);
+
+/* ---- plan: adapter-index gather and segment bookkeeping -----------------------------
+ * The plan is a device-resident table built from the per-token adapter ids: a stable
+ * counting sort (token order kept inside one adapter), the segment list, and the work
+ * units the kernels walk.  One plan serves every layer and projection of a step.
+ * Replaces the reference's per-call index tensor `select_inds[bsz-1]`
+ * (lightllm/models/lora_gpu.py:120,124). */
+size_t b200_lora_plan_bytes(int32_t max_tokens, int32_t n_adapters);
+
+/* `max_tokens` is the capacity the plan buffer was sized for (n_tokens <= max_tokens); the
+ * same value is passed to b200_lora_apply and sizes the workspace. */
+/* ids: device [T], int32 (ids_are_i64 == 0) or int64.  ranks as in b200_lora_adapters. */
+int b200_lora_plan_build(void* plan, size_t plan_bytes, int32_t max_tokens, const void* ids,
+                         int32_t ids_are_i64, int32_t n_tokens, const b200_lora_adapters* adapters,
+                         void* stream);
+
+/* Rows of x are already grouped: segment s covers rows [seg_starts[s], seg_starts[s+1]) and
+ * uses adapter seg_adapter[s].  Both arrays are device int32; n_segs is a host value. */
+int b200_lora_plan_from_segments(void* plan, size_t plan_bytes, int32_t max_tokens,
+                                 const int32_t* seg_starts, const int32_t* seg_adapter, int32_t n_segs,
+                                 int32_t n_tokens, const b200_lora_adapters* adapters, void* stream);
+
+/* Copies the plan's tables to host arrays (synchronises `stream`): perm [T], seg_starts
+ * [T+1], seg_adapter [T]; *n_segs receives S.  Returns B200_LORA_ERR_ID_RANGE if the build
+ * saw an id outside [0, N) (such a plan applies nothing). */
+int b200_lora_plan_read(const void* plan, int32_t* perm, int32_t* seg_starts, int32_t* seg_adapter,
+                        int32_t* n_segs, int32_t* n_tokens, void* stream);
+
+/* ---- apply ---------------------------------------------------------------------------- */
+size_t b200_lora_workspace_bytes(int32_t max_tokens, int32_t n_proj, int32_t max_h_in);
+/* Zero-fills a fresh workspace; call once per allocation, before its first use.  The
+ * kernels leave the control words zero again when they finish. */
+int b200_lora_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Applies the delta of `layer` to up to B200_LORA_MAX_PROJ projections in one pass.
+ * io_dtype: type of x, wa, wb (F16 | BF16).  y_dtype: io_dtype or F32. */
+int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
+                    const void* plan, int32_t max_tokens, int32_t layer, int32_t io_dtype,
+                    int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* ---- the reference's operator call -------------------------------------------------------
+ * Same arguments as punica.ops.add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx,
+ * scale) at lightllm/models/lora_gpu.py:138,150,162, flattened to pointers and sizes.
+ * Builds a plan inside `workspace` and applies one projection.  `workspace` must have been
+ * zero-filled once (b200_lora_workspace_init) after allocation. */
+size_t b200_add_lora_bgmv_workspace_bytes(int32_t n_tokens, int32_t n_adapters, int32_t h_in);
+int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void* wb_T_all,
+                       const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
+                       int32_t h_in, int32_t h_out, int32_t n_adapters, int32_t n_layers, int32_t r,
+                       int32_t layer_idx, float scale, int32_t dtype,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_LORA_H */

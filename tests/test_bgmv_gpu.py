@@ -1,0 +1,121 @@
+"""GPU parity of the decode BGMV path against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import ae296_b200 as L
+from lora_testlib import TOL, Case, rel_err
+from oracle import lora_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T", [1, 2, 31, 33])
+@pytest.mark.parametrize("r", [8, 16, 64])
+@pytest.mark.parametrize("H", [128, 4096])
+def test_tiny_exhaustive(T, r, H):
+    c = Case(T, 5, H, H, r, "fp16", dense=False, seed=T * 100 + r + H)
+    want = c.oracle_delta(1)
+    y32 = c.run(1, y_dtype=torch.float32)
+    assert rel_err(y32.double().cpu().numpy(), want) <= TOL
+    y16 = c.run(1)
+    # the low-precision output is the single rounding of the fp32 result
+    assert torch.equal(y16, y32.to(torch.float16))
+    # a second run is bit-identical (fixed-order split-K reduction, no float atomics)
+    assert torch.equal(c.run(1, y_dtype=torch.float32), y32)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("dense", [False, True])
+def test_mixed_ranks_both_layouts(dtype, dense):
+    c = Case(96, 24, 1024, 768, [8, 16, 32, 64], dtype, dense=dense, seed=7, zipf=1.0)
+    for layer in (0, 1):
+        want = c.oracle_delta(layer)
+        y32 = c.run(layer, y_dtype=torch.float32)
+        assert rel_err(y32.double().cpu().numpy(), want) <= TOL
+        assert torch.equal(c.run(layer), y32.to(c.tdt))
+
+
+def test_dense_pool_ranks_not_multiple_of_8_and_garbage_padding():
+    c = Case(40, 6, 512, 512, np.array([3, 12, 20, 33, 50, 64], np.int32), "fp16", dense=True, seed=3)
+    # poison the unused rows/columns of the dense pool: they must never be read into the result
+    for a in range(c.N):
+        r = int(c.ranks[a])
+        c.pool.wa[a, :, r:, :] = float("nan")
+        c.pool.wb[a, :, :, r:] = float("nan")
+    y32 = c.run(0, y_dtype=torch.float32)
+    assert rel_err(y32.double().cpu().numpy(), c.oracle_delta(0)) <= TOL
+
+
+def test_accumulates_into_y_with_strides_and_canaries():
+    c = Case(37, 9, 640, 384, [16, 32], "bf16", seed=11)
+    g = torch.Generator().manual_seed(5)
+    pad = 16
+    ybig = torch.randn(c.T + 2, c.h_out + 2 * pad, generator=g).to(torch.bfloat16).cuda()
+    before = ybig.clone()
+    xbig = torch.full((c.T, c.h_in + 24), 7.0, dtype=torch.bfloat16, device="cuda")
+    xbig[:, :c.h_in] = c.x
+    yv = ybig[1:-1, pad:pad + c.h_out]
+    batch = L.LoraBatch(c.T, c.N, c.h_in, 1).set_ids(c.ids_dev, c.pool)
+    batch.apply([(xbig[:, :c.h_in], yv, c.pool)], 1)
+    torch.cuda.synchronize()
+    want = O.round_to(before[1:-1, pad:pad + c.h_out].double().cpu().numpy() + c.oracle_delta(1), "bf16")
+    got = yv.double().cpu().numpy()
+    rms = np.sqrt((want ** 2).mean())
+    # one bf16 rounding of (y + delta): within half an ulp of the exact sum plus the fp32 error
+    assert np.abs(got - want).max() <= np.abs(want).max() * 2 ** -8 + TOL * rms
+    mask = torch.ones_like(ybig, dtype=torch.bool)
+    mask[1:-1, pad:pad + c.h_out] = False
+    assert torch.equal(ybig[mask], before[mask]), "bytes outside the y view were written"
+
+
+def test_reference_call_signature_int64_ids():
+    c = Case(32, 8, 4096, 4096, 16, "fp16", dense=True, seed=2960)
+    y = torch.zeros(c.T, c.h_out, dtype=torch.float16, device="cuda")
+    ret = L.add_lora_bgmv(y, c.x, c.pool.wa, c.pool.wb, c.ids_dev.long(), 1, 2.0)
+    torch.cuda.synchronize()
+    assert ret is None
+    want = O.lora_delta(c.x_cpu.double().numpy(), lambda a: c.A[a][1].double().numpy(),
+                        lambda a: c.B[a][1].double().numpy(), c.ids, np.full(c.N, 2.0))
+    got = y.double().cpu().numpy()
+    rms = np.sqrt((want ** 2).mean())
+    assert np.abs(got - want).max() <= TOL * rms + np.abs(want).max() * 2 ** -11
+
+
+def test_mid_round_flag_matches_bmm_rounding():
+    c = Case(64, 4, 512, 512, 32, "fp16", seed=9, ids=np.repeat(np.arange(4), 16))
+    y32 = c.run(0, y_dtype=torch.float32, flags=L.MID_ROUND)
+    assert rel_err(y32.double().cpu().numpy(), c.oracle_delta(0, mid_round="fp16")) <= TOL
+
+
+def test_fused_qkv_equals_separate_calls():
+    c = Case(48, 12, 1024, 1024, [8, 64], "fp16", seed=21, zipf=1.0)
+    k = Case(48, 12, 1024, 256, c.ranks, "fp16", seed=22, ids=c.ids)
+    ys = [torch.zeros(48, h, dtype=torch.float16, device="cuda") for h in (1024, 256, 1024)]
+    batch = L.LoraBatch(48, 12, 1024, 3).set_ids(c.ids_dev, c.pool)
+    batch.apply([(c.x, ys[0], c.pool), (c.x, ys[1], k.pool), (c.x, ys[2], c.pool)], 1)
+    torch.cuda.synchronize()
+    assert torch.equal(ys[0], c.run(1))
+    assert torch.equal(ys[2], ys[0])
+    k.x, k.x_cpu = c.x, c.x_cpu
+    assert torch.equal(ys[1], k.run(1))
+
+
+def test_errors_are_raised_not_swallowed():
+    c = Case(8, 4, 128, 128, 8, "fp16", seed=1)
+    bad = c.ids_dev.clone()
+    bad[3] = 4                      # == N: out of range
+    batch = L.LoraBatch(8, 4, 128, 1)
+    batch.plan.build(bad, L.adapters_of(c.pool))
+    with pytest.raises(L.LoraError) as e:
+        batch.plan.read()
+    assert e.value.code == -8
+    # such a plan applies nothing
+    y = torch.zeros(8, 128, dtype=torch.float16, device="cuda")
+    batch.apply([(c.x, y, c.pool)], 0)
+    torch.cuda.synchronize()
+    assert not y.any()
+    with pytest.raises(L.LoraError):
+        batch.set_ids(c.ids_dev, c.pool).apply([(c.x, y, c.pool)], 5)       # layer out of range
+    with pytest.raises(ValueError):
+        L.add_lora_bgmv(y.cpu(), c.x.cpu(), c.pool.wa.cpu(), c.pool.wb.cpu(), c.ids_dev.cpu(), 0, 1.0)
