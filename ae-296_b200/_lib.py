@@ -34,7 +34,7 @@ class LoraError(RuntimeError):
 class Adapters(C.Structure):
     _fields_ = [("ranks", C.c_void_p), ("scalings", C.c_void_p), ("cum_ranks", C.c_void_p),
                 ("n_adapters", C.c_int32), ("n_layers", C.c_int32), ("r_pool", C.c_int32),
-                ("packed", C.c_int32), ("scale", C.c_float)]
+                ("packed", C.c_int32), ("scale", C.c_float), ("ranks_pow2", C.c_int32)]
 
 
 class Proj(C.Structure):
@@ -55,6 +55,7 @@ SYMBOLS = {
                                       C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_void_p]),
     "b200_lora_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "b200_lora_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200_lora_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_lora_apply": (C.c_int, [C.POINTER(Proj), C.c_int32, C.POINTER(Adapters), C.c_void_p, C.c_int32,
                                   C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t,
                                   C.c_void_p]),

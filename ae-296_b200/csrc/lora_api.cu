@@ -40,6 +40,26 @@ int check_adapters(const b200_lora_adapters* ad) {
     return B200_LORA_OK;
 }
 
+// true when the TMA kernels may be used as far as ranks are concerned
+bool fast_ranks(const b200_lora_adapters* ad) {
+    const int r = ad->r_pool;
+    const bool pow2 = (r == 8 || r == 16 || r == 32 || r == 64);
+    if (!ad->packed && !ad->ranks) return pow2;
+    return ad->ranks_pow2 != 0 && (ad->packed || pow2);
+}
+
+PlanAdapters plan_adapters(const b200_lora_adapters* ad) {
+    PlanAdapters pa;
+    pa.ranks = ad->ranks;
+    pa.cum_ranks = ad->packed ? reinterpret_cast<const long long*>(ad->cum_ranks) : nullptr;
+    pa.scalings = ad->scalings;
+    pa.scale = ad->scale;
+    pa.r_pool = ad->r_pool;
+    pa.n_adapters = ad->n_adapters;
+    pa.ranks_pow2 = fast_ranks(ad) ? 1 : 0;
+    return pa;
+}
+
 }  // namespace
 
 extern "C" {
@@ -63,8 +83,8 @@ int b200_lora_plan_build(void* plan, size_t plan_bytes, int32_t max_tokens, cons
     const int cap = max_tokens;
     if (plan_bytes < b200_lora_plan_bytes(cap, adapters->n_adapters)) return B200_LORA_ERR_WORKSPACE;
     if (!aligned16(plan)) return B200_LORA_ERR_ALIGN;
-    cudaError_t e = launch_plan_build(plan, cap, ids, ids_are_i64, n_tokens, adapters->ranks, adapters->r_pool,
-                                      adapters->n_adapters, static_cast<cudaStream_t>(stream));
+    cudaError_t e = launch_plan_build(plan, cap, ids, ids_are_i64, n_tokens, plan_adapters(adapters),
+                                      static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }
 
@@ -79,8 +99,7 @@ int b200_lora_plan_from_segments(void* plan, size_t plan_bytes, int32_t max_toke
     if (plan_bytes < b200_lora_plan_bytes(cap, adapters->n_adapters)) return B200_LORA_ERR_WORKSPACE;
     if (!aligned16(plan)) return B200_LORA_ERR_ALIGN;
     cudaError_t e = launch_plan_from_segments(plan, cap, seg_starts, seg_adapter, n_segs, n_tokens,
-                                              adapters->ranks, adapters->r_pool, adapters->n_adapters,
-                                              static_cast<cudaStream_t>(stream));
+                                              plan_adapters(adapters), static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }
 
@@ -95,6 +114,7 @@ int b200_lora_plan_read(const void* plan, int32_t* perm, int32_t* seg_starts, in
     *n_segs = h.n_segs;
     *n_tokens = h.n_tokens;
     if (h.error == 1) return B200_LORA_ERR_ID_RANGE;
+    if (h.error == 3) return B200_LORA_ERR_RANK;
     if (h.error) return B200_LORA_ERR_SEGMENTS;
     PlanView pv = plan_view(const_cast<void*>(plan), h.cap, h.n_adapters);
     if (perm) e = cudaMemcpyAsync(perm, pv.perm, 4 * (size_t)h.n_tokens, cudaMemcpyDeviceToHost, s);
@@ -170,8 +190,21 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     cudaError_t e = cudaSuccess;
     if (!sgmv_tiles_supported(p)) p.flags |= B200_LORA_NO_TENSOR;
     if (!(p.flags & B200_LORA_NO_TENSOR)) e = launch_sgmv_tiles(p, io_dtype, n_sm, s);
-    if (e == cudaSuccess) e = launch_bgmv(p, io_dtype, n_sm, s);
+    bool fast = fast_ranks(adapters);
+    for (int i = 0; i < n_proj; ++i)
+        if ((projs[i].h_in % 256) || (projs[i].h_out % 256)) fast = false;
+    if (e == cudaSuccess) e = fast ? launch_bgmv_tma(p, io_dtype, n_sm, s) : launch_bgmv(p, io_dtype, n_sm, s);
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_workspace_status(const void* workspace, void* stream) {
+    if (!workspace) return B200_LORA_ERR_NULL;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    WorkspaceCtl ctl;
+    cudaError_t e = cudaMemcpyAsync(&ctl, workspace, sizeof(ctl), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return ctl.error ? B200_LORA_ERR_TIMEOUT : B200_LORA_OK;
 }
 
 size_t b200_add_lora_bgmv_workspace_bytes(int32_t n_tokens, int32_t n_adapters, int32_t h_in) {

@@ -1,12 +1,20 @@
-// Decode BGMV: shrink (v = x . A^T) and expand (y += scale * v . B^T) on adapter-sorted segments.
+// Decode BGMV: shrink (v = x . A^T) and expand (y += scale * v . B^T) on adapter-sorted work
+// segments of at most 8 tokens.
 //
-// Both kernels are HBM-bound weight streamers.  Work is cut into units of 32 KB of weights
-// (8 independent 128-bit loads per thread, 256 threads): the number of k-columns (shrink) or
-// output rows (expand) per unit shrinks as the rank grows, so every unit costs the same bytes.
-// A segment's weights are read from HBM once and applied to all of its tokens, four tokens per
-// register pass.  fp32 accumulation throughout; cross-lane sums use a halving butterfly of warp
-// shuffles.  The split-K partial sums of the shrink are combined in a fixed order by the last
-// CTA to arrive at a per-(projection, segment) counter, so results are bit-reproducible.
+// Both kernels are HBM-bound weight streamers built the same way: one persistent CTA per SM
+// walks 32 KB weight units through a 4-stage shared-memory ring filled with 128-bit cp.async
+// loads (weights, the unit's activation rows, and for the expand the y tile it will update),
+// so ~100 KB of loads per SM are in flight while earlier units are being computed.  Tiles are
+// XOR-swizzled at 16-byte granularity so ldmatrix reads are conflict-free, and the arithmetic
+// is mma.sync m16n8k16 with the unit's <= 8 tokens as (half of) the M dimension, weight rows as
+// N, and fp32 accumulators.
+// The unit size is constant in bytes: the k-columns (shrink) or output rows (expand) per unit
+// shrink as the rank grows.  A segment's weights are read from HBM once for all its tokens.
+//
+// The split-K partial sums of the shrink are folded in a fixed order by the CTA that arrives
+// last at a per-(projection, work segment) counter, so results are bit-reproducible; the
+// arrival's round trip is hidden behind the next unit's work.  The expand keeps the fp32
+// intermediate exact to ~2^-22 by feeding it to the tensor cores as a hi + lo pair.
 //
 // Semantics follow the call `add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx, scale)`
 // of the reference (lightllm/models/lora_gpu.py:138,150,162) with pools laid out as at :33-40.
@@ -16,353 +24,557 @@ namespace b200lora {
 
 namespace {
 
-__device__ __forceinline__ uint4 zero4() { return make_uint4(0u, 0u, 0u, 0u); }
+constexpr int kStages = 4;
+constexpr int kMetaSlots = 8;
+constexpr int kWBytes = 32768;                 // weights of one unit
+constexpr int kXBytes = 16384;                 // shrink: 8 tokens x <= 1024 columns
+constexpr int kYPitchPad = 16;                 // bytes added to a y-tile row against bank conflicts
+constexpr int kYBytes = 8 * (1024 * 2 + kYPitchPad);
+constexpr int kVPitch = 72;                    // floats per token row of the v tile
+constexpr int kVBytes = 8 * kVPitch * 4;
+constexpr int kShrinkStage = kWBytes + kXBytes;
+constexpr int kExpandStage = kWBytes + kYBytes + kVBytes;
+constexpr int kWarps = kCtaThreads / 32;       // 16
+constexpr int kRedBytes = 8 * 8 * 68 * 4;      // largest cross-warp reduction tile (rank 64: 8 k-slots)
 
-// keep the first `nvalid` 16-bit lanes of a 128-bit word, clear the rest
-__device__ __forceinline__ uint4 mask_lanes(uint4 u, int nvalid) {
-    if (nvalid >= 8) return u;
-    if (nvalid <= 0) return zero4();
-    unsigned* w = reinterpret_cast<unsigned*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        int lo = 2 * i, hi = 2 * i + 1;
-        unsigned m = (lo < nvalid ? 0x0000ffffu : 0u) | (hi < nvalid ? 0xffff0000u : 0u);
-        w[i] &= m;
-    }
-    return u;
+struct Meta {               // per in-flight unit, in shared memory
+    UnitRec u;
+    int proj, c0;           // projection and first column (shrink) / row (expand) of the unit
+    int valid;              // 0: the unit's range lies outside the projection
+    int kc;                 // split-K chunk index (shrink)
+    int n_chunks;           // split-K chunk count of this (projection, work segment)
+    int pad[3];
+};
+static_assert(sizeof(Meta) == 96, "meta slot");
+
+// ---- small PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(unsigned addr, unsigned& r0, unsigned& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
 
-// Sum NV per-lane values over groups of G consecutive lanes.  Afterwards lane g (within its
-// group) holds the NV/G totals with original indices [g*NV/G, (g+1)*NV/G) in v[0 .. NV/G).
-// If NV < G the remaining steps are plain all-reduces and every lane of a sub-group holds
-// the same single total.
-template <int NV, int G>
-__device__ __forceinline__ void halving_reduce(float (&v)[NV], int lane) {
-    int n = NV;
-#pragma unroll
-    for (int o = G / 2; o >= 1; o >>= 1) {
-        if (n > 1) {
-            n >>= 1;
-            const bool hi = (lane & o) != 0;
-#pragma unroll
-            for (int i = 0; i < NV / 2; ++i) {
-                if (i < n) {
-                    float send = hi ? v[i] : v[i + n];
-                    float keep = hi ? v[i + n] : v[i];
-                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-                }
-            }
-        } else {
-            v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
-        }
+template <typename T> struct Mma;
+template <> struct Mma<__half> {
+    static __device__ __forceinline__ void run(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     }
-}
-
-struct Item {
-    int seg, sub, proj, super;
+};
+template <> struct Mma<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
 };
 
-// item -> (unit, projection, super-chunk); n_super[] per projection
-__device__ __forceinline__ Item decode_item(const ApplyParams& p, const PlanView& pv, int it, int n_units,
-                                            bool expand) {
-    Item r;
-    int u = it % n_units;
+__device__ __forceinline__ unsigned atom_add_acq_rel(unsigned* p, unsigned v) {
+    unsigned old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+
+// item -> (unit, projection, super-chunk)
+__device__ __forceinline__ void decode_item(const ApplyParams& p, int it, int n_units, bool expand,
+                                            int& unit, int& proj, int& super) {
+    unit = it % n_units;
     int sp = it / n_units;
     int pi = 0;
 #pragma unroll
     for (int i = 0; i < kMaxProj; ++i) {
-        int ns = expand ? p.proj[i].n_super_out : p.proj[i].n_super_in;
-        if (i < p.n_proj && sp >= ns && pi == i) { sp -= ns; pi = i + 1; }
+        const int ns = expand ? p.proj[i].n_super_out : p.proj[i].n_super_in;
+        if (i < p.n_proj - 1 && pi == i && sp >= ns) { sp -= ns; pi = i + 1; }
     }
-    int e = pv.unit_tab[u];
-    r.seg = e >> 3;
-    r.sub = e & 7;
-    r.proj = pi;
-    r.super = sp;
-    return r;
+    proj = pi;
+    super = sp;
 }
 
-// ---------------------------------------------------------------------------------------------
-// shrink: one unit = rows [0, r) x KC columns of A_a, KC = 16384 / r_pad
-// ---------------------------------------------------------------------------------------------
-template <typename T, int RPW>
-__device__ void shrink_item(const ApplyParams& p, const PlanView& pv, const WorkspaceView& ws, const Item it,
-                            int* s_flag) {
-    constexpr int KS = kSlots / RPW;            // k-steps of 256 columns per unit
-    constexpr int KC = KS * 256;
-    constexpr int RPAD = RPW * 8;
-    constexpr int NV = RPW * kTokTile;
-    const ProjArgs& pj = p.proj[it.proj];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int k0 = it.super * kSuper + it.sub * KC;
-    if (k0 >= pj.h_in) return;
-    const int a = pv.seg_adapter[it.seg];
-    const int r = pv.seg_rank[it.seg];
-    const int b = pv.seg_start[it.seg], e = pv.seg_start[it.seg + 1];
-    const T* A = reinterpret_cast<const T*>(pj.wa) + block_row0(p, a, r) * (long long)pj.h_in;
+// Starts the load of one item's unit record (warp 0; lanes 0..15 carry one word each).
+__device__ __forceinline__ void fetch_meta_regs(const ApplyParams& p, const PlanView& pv, int it, int n_units,
+                                                bool expand, int lane, int& word, int& proj, int& super) {
+    int unit;
+    decode_item(p, it, n_units, expand, unit, proj, super);
+    word = 0;
+    if (lane < 16) word = __ldg(pv.unit_tab + (size_t)unit * 16 + lane);
+}
 
-    uint4 w[kSlots];
-#pragma unroll
-    for (int q = 0; q < kSlots; ++q) {
-        const int rl = q % RPW, ks = q / RPW;
-        const int i = warp * RPW + rl;
-        const int k = k0 + ks * 256 + lane * 8;
-        w[q] = (i < r && k < pj.h_in) ? ldg_nc16(A + (long long)i * pj.h_in + k) : zero4();
+__device__ __forceinline__ void store_meta(const ApplyParams& p, Meta* m, int lane, int word, int proj, int super,
+                                           bool expand) {
+    if (lane < 16) reinterpret_cast<int*>(&m->u)[lane] = word;
+    __syncwarp();
+    if (lane == 0) {
+        const int r_pad = pad_rank(m->u.rank);
+        const int width = kSuper / n_sub(r_pad);
+        const int c0 = super * kSuper + m->u.sub * width;
+        const int h = expand ? p.proj[proj].h_out : p.proj[proj].h_in;
+        m->proj = proj;
+        m->c0 = c0;
+        m->valid = c0 < h;
+        m->kc = c0 / width;
+        m->n_chunks = (p.proj[proj].h_in + width - 1) / width;
     }
+}
 
-    const int kc = k0 / KC;
-    const T* X = reinterpret_cast<const T*>(pj.x);
-    for (int pos0 = b; pos0 < e; pos0 += kTokTile) {
-        const int nt = min(kTokTile, e - pos0);
-        float acc[NV];
+// =============================================================================================
+// shrink
+// =============================================================================================
+// Shared tile of A: r16 = max(r_pad, 16) rows x KC columns, row pitch KC*2 bytes, 16-byte chunk
+// c of row i stored at chunk (c ^ (i & 7)).  The x tile uses the same layout with row = token.
+template <typename T>
+__device__ __forceinline__ void shrink_issue(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid) {
+    if (!m.valid) return;
+    const ProjArgs& pj = p.proj[m.proj];
+    const int r = m.u.rank, r_pad = pad_rank(r);
+    const int kc_cols = kSuper / n_sub(r_pad);           // 1024, 1024, 512, 256
+    const int cpr = kc_cols / 8;                         // 16-byte chunks per row: 128, 128, 64, 32
+    const int cpr_shift = 31 - __clz(cpr);
+    const int pitch = kc_cols * 2;
+    const T* A = reinterpret_cast<const T*>(pj.wa) + block_row0(p, m.u) * (long long)pj.h_in + m.c0;
+    const unsigned wbase = smem_u32(stage);
+    // thread -> (row0, c); successive chunks of a thread are rstep rows apart
+    const int c = tid & (cpr - 1), row0 = tid >> cpr_shift, rstep = kCtaThreads >> cpr_shift;
+    const bool col_ok = (m.c0 + c * 8) < pj.h_in;
+    for (int row = row0; row < r_pad; row += rstep) {
+        const bool ok = col_ok && row < r;
+        const T* src = ok ? A + row * pj.h_in + c * 8 : reinterpret_cast<const T*>(pj.wa);
+        cp_async16(wbase + row * pitch + ((c ^ (row & 7)) << 4), src, ok ? 16 : 0);
+    }
+    const T* X = reinterpret_cast<const T*>(pj.x) + m.c0 + c * 8;
+    const unsigned xbase = wbase + kWBytes;
+    for (int row = row0; row < m.u.ntok; row += rstep) {
+        const T* src = col_ok ? X + (long long)m.u.tok[row] * pj.ldx : reinterpret_cast<const T*>(pj.x);
+        cp_async16(xbase + row * pitch + ((c ^ (row & 7)) << 4), src, col_ok ? 16 : 0);
+    }
+}
+
+// Tokens are the M rows of the MMA (rows 8..15 are zero), weight rows the N columns, so each
+// thread ends up with two adjacent ranks of one token.  16 warps = (1 or 2 halves of the rank
+// blocks) x (16 or 8 slices of the unit's columns); slices are summed through shared memory.
+template <typename T>
+__device__ __forceinline__ void shrink_compute(const ApplyParams& p, const WorkspaceView& ws, const Meta& m,
+                                               unsigned char* stage, float* red, int tid) {
+    if (!m.valid) return;                                  // uniform across the CTA
+    const int lane = tid & 31, warp = tid >> 5;
+    const int r_pad = pad_rank(m.u.rank);
+    const int NB = r_pad / 8;                              // 8-row weight blocks: 1, 2, 4, 8
+    const int nsplit = NB >= 2 ? 2 : 1;
+    const int ksplit = kWarps / nsplit;                    // 16 or 8
+    const int NBW = NB / nsplit;                           // blocks per warp: 1, 1, 2, 4
+    const int kc_cols = kSuper / n_sub(r_pad);
+    const int pitch = kc_cols * 2;
+    const int kslot = warp % ksplit, nhalf = warp / ksplit;
+    const int nk16 = kc_cols / 16 / ksplit;                // k16 steps per warp: 4, 8, 4, 2
+    const int cw = kslot * nk16 * 2;                       // first 16-byte chunk of this warp
+    const unsigned wbase = smem_u32(stage), xbase = wbase + kWBytes;
+    const int rp = r_pad + 4;                              // pitch of a reduction row
+    float acc[4][4];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) acc[i] = 0.f;
-        int tok[kTokTile];
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int tt = 0; tt < kTokTile; ++tt) tok[tt] = pv.perm[pos0 + (tt < nt ? tt : 0)];
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    const int l7 = lane & 7, mi = lane >> 3;
+    for (int ks = 0; ks < nk16; ++ks) {
+        const int c = cw + 2 * ks;
+        unsigned a0, a2;
+        ldmatrix_x2(xbase + l7 * pitch + (((c + (mi & 1)) ^ l7) << 4), a0, a2);
+        if (NBW == 1) {
+            const int row = nhalf * 8 + l7;
+            unsigned b0, b1;
+            ldmatrix_x2(wbase + row * pitch + (((c + (mi & 1)) ^ (row & 7)) << 4), b0, b1);
+            Mma<T>::run(acc[0], a0, 0u, a2, 0u, b0, b1);
+        } else {
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            const int k = k0 + ks * 256 + lane * 8;
-            float xf[kTokTile][8];
-#pragma unroll
-            for (int tt = 0; tt < kTokTile; ++tt) {
-                uint4 xv = (tt < nt && k < pj.h_in) ? ldg16(X + (long long)tok[tt] * pj.ldx + k) : zero4();
-                Cvt<T>::unpack8(xv, xf[tt]);
-            }
-#pragma unroll
-            for (int rl = 0; rl < RPW; ++rl) {
-                float wf[8];
-                Cvt<T>::unpack8(w[ks * RPW + rl], wf);
-#pragma unroll
-                for (int tt = 0; tt < kTokTile; ++tt) {
-                    if (tt < nt) {
-                        float s = acc[rl * kTokTile + tt];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) s = fmaf(wf[j], xf[tt][j], s);
-                        acc[rl * kTokTile + tt] = s;
-                    }
+            for (int pr = 0; pr < 2; ++pr) {
+                if (2 * pr < NBW) {
+                    const int row = (nhalf * NBW + 2 * pr + (mi >> 1)) * 8 + l7;
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4(wbase + row * pitch + (((c + (mi & 1)) ^ (row & 7)) << 4), b0, b1, b2, b3);
+                    Mma<T>::run(acc[2 * pr], a0, 0u, a2, 0u, b0, b1);
+                    Mma<T>::run(acc[2 * pr + 1], a0, 0u, a2, 0u, b2, b3);
                 }
             }
         }
-        halving_reduce<NV, 32>(acc, lane);
-        // writer lanes: low (5 - log2 NV) bits clear; value index = lane >> (5 - log2 NV)
-        constexpr int SH = (NV == 32) ? 0 : (NV == 16) ? 1 : (NV == 8) ? 2 : 3;
-        if ((lane & ((1 << SH) - 1)) == 0) {
-            const int vi = lane >> SH;
-            const int rl = vi / kTokTile, tt = vi % kTokTile;
-            if (tt < nt) {
-                const int i = warp * RPW + rl;
-                ws.partial[(((size_t)kc * p.n_proj + it.proj) * p.cap + (pos0 + tt)) * kMaxRank + i] = acc[0];
-            }
+    }
+    // red[kslot][token][rank]: token g, ranks (block*8 + 2t, +1)
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (i < NBW) {
+            float2* dst = reinterpret_cast<float2*>(red + (kslot * 8 + g) * rp + (nhalf * NBW + i) * 8 + 2 * t);
+            *dst = make_float2(acc[i][0], acc[i][1]);
         }
     }
+    __syncthreads();
+    // fold the column slices in slice order and publish this unit's split-K partial
+    const int outs = m.u.ntok * r_pad;
+    for (int idx = tid; idx < outs; idx += kCtaThreads) {
+        const int tok = idx / r_pad, i = idx % r_pad;
+        float s = 0.f;
+        for (int w = 0; w < ksplit; ++w) s += red[(w * 8 + tok) * rp + i];
+        ws.partial[(((size_t)m.kc * p.n_proj + m.proj) * p.cap + (m.u.start + tok)) * kMaxRank + i] = s;
+    }
+}
 
-    // arrive; the last CTA of this (projection, segment) folds the partials in k order
-    const int n_chunks = (pj.h_in + KC - 1) / KC;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        unsigned old = atomicAdd(&ws.counters[(size_t)it.proj * p.cap + it.seg], 1u);
-        *s_flag = (old == (unsigned)(n_chunks - 1));
-    }
-    __syncthreads();
-    if (*s_flag) {
-        __threadfence();
-        const int len = e - b;
-        const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
-        for (int idx = tid; idx < len * RPAD; idx += kCtaThreads) {
-            const int pos = b + idx / RPAD, i = idx % RPAD;
-            float s = 0.f;
-            for (int c = 0; c < n_chunks; ++c)
-                s += __ldcg(&ws.partial[(((size_t)c * p.n_proj + it.proj) * p.cap + pos) * kMaxRank + i]);
-            if (mid_round) s = Cvt<T>::round1(s);
-            ws.v[((size_t)it.proj * p.cap + pos) * kMaxRank + i] = s;
+// The CTA that arrived last folds all split-K partials of one (projection, work segment) in k order.
+template <typename T>
+__device__ __forceinline__ void shrink_fold(const ApplyParams& p, const WorkspaceView& ws, const Meta& m, int tid) {
+    const int r_pad = pad_rank(m.u.rank);
+    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
+    const int outs = m.u.ntok * r_pad;
+    for (int idx = tid; idx < outs; idx += kCtaThreads) {
+        const int pos = m.u.start + idx / r_pad, i = idx % r_pad;
+        const float* src = &ws.partial[((size_t)m.proj * p.cap + pos) * kMaxRank + i];
+        const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
+        float s = 0.f;
+        int c = 0;
+        for (; c + 8 <= m.n_chunks; c += 8) {            // 8 loads in flight, summed in k order
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + (size_t)(c + j) * cstride);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += v[j];
         }
-        if (tid == 0) ws.counters[(size_t)it.proj * p.cap + it.seg] = 0u;
+        for (; c < m.n_chunks; ++c) s += __ldcg(src + (size_t)c * cstride);
+        if (mid_round) s = Cvt<T>::round1(s);
+        ws.v[((size_t)m.proj * p.cap + pos) * kMaxRank + i] = s;
     }
-    __syncthreads();
+    if (tid == 0) ws.counters[(size_t)m.proj * p.cap + m.u.wseg] = 0u;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kCtaThreads, 2) bgmv_shrink_kernel(const __grid_constant__ ApplyParams p) {
-    __shared__ int s_item;
-    __shared__ int s_flag;
+__global__ void __launch_bounds__(kCtaThreads, 1) bgmv_shrink_kernel(const __grid_constant__ ApplyParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* stages = smem;
+    float* red = reinterpret_cast<float*>(smem + kStages * kShrinkStage);   // 8 or 16 slices x 8 tokens x (r_pad + 4)
+    Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kShrinkStage + kRedBytes);
+    int* s_fold = reinterpret_cast<int*>(meta + kMetaSlots);
+
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
     if (hdr.error || hdr.cap != p.cap) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_in;
-    while (true) {
-        if (threadIdx.x == 0) s_item = (int)atomicAdd(&ws.ctl->ticket[0], 1u);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int first = blockIdx.x, stride = gridDim.x;
+    if (first >= n_items) return;
+    const int n_local = (n_items - first + stride - 1) / stride;
+
+    // prologue: metadata of the first kStages items (one warp each), loads of the first kStages - 1
+    if (warp < kStages && warp < n_local) {
+        int word, proj, super;
+        fetch_meta_regs(p, pv, first + warp * stride, n_units, false, lane, word, proj, super);
+        store_meta(p, &meta[warp % kMetaSlots], lane, word, proj, super, false);
+    }
+    if (tid == 0) *s_fold = -1;
+    __syncthreads();
+    for (int n = 0; n < kStages - 1; ++n) {
+        if (n < n_local) shrink_issue<T>(p, meta[n % kMetaSlots], stages + (n % kStages) * kShrinkStage, tid);
+        cp_async_commit();
+    }
+
+    unsigned ticket = 0;          // thread 0: arrival count returned for the previous item
+    for (int n = 0; n < n_local; ++n) {
+        // fold a segment whose last arrival was ours (decided before the previous barrier)
+        const int fold_slot = *s_fold;
+        if (fold_slot >= 0) shrink_fold<T>(p, ws, meta[fold_slot], tid);
+        // arrive for item n-1: its partials were written before the barrier that ended iteration n-1
+        const bool arrive = n > 0 && meta[(n - 1) % kMetaSlots].valid;
+        if (tid == 0 && arrive) {
+            const Meta& pm = meta[(n - 1) % kMetaSlots];
+            ticket = atom_add_acq_rel(&ws.counters[(size_t)pm.proj * p.cap + pm.u.wseg], 1u);
+        }
+        const int nn = n + kStages - 1;
+        if (nn < n_local) shrink_issue<T>(p, meta[nn % kMetaSlots], stages + (nn % kStages) * kShrinkStage, tid);
+        cp_async_commit();
+        int word = 0, mproj = 0, msuper = 0;
+        const int nm = n + kStages;
+        if (warp == 0 && nm < n_local) fetch_meta_regs(p, pv, first + nm * stride, n_units, false, lane, word, mproj, msuper);
+        cp_async_wait<kStages - 1>();
         __syncthreads();
-        const int it = s_item;
+        shrink_compute<T>(p, ws, meta[n % kMetaSlots], stages + (n % kStages) * kShrinkStage, red, tid);
+        if (warp == 0 && nm < n_local) store_meta(p, &meta[nm % kMetaSlots], lane, word, mproj, msuper, false);
+        if (tid == 0) {
+            int f = -1;
+            if (arrive && ticket == (unsigned)(meta[(n - 1) % kMetaSlots].n_chunks - 1)) f = (n - 1) % kMetaSlots;
+            *s_fold = f;
+        }
         __syncthreads();
-        if (it >= n_items) break;
-        Item item = decode_item(p, pv, it, n_units, false);
-        const int rpad = pad_rank(pv.seg_rank[item.seg]);
-        switch (rpad) {
-            case 8:  shrink_item<T, 1>(p, pv, ws, item, &s_flag); break;
-            case 16: shrink_item<T, 2>(p, pv, ws, item, &s_flag); break;
-            case 32: shrink_item<T, 4>(p, pv, ws, item, &s_flag); break;
-            default: shrink_item<T, 8>(p, pv, ws, item, &s_flag); break;
+    }
+    // drain: a pending fold, then the arrival (and possible fold) of the last item
+    const int last_fold = *s_fold;
+    if (last_fold >= 0) shrink_fold<T>(p, ws, meta[last_fold], tid);
+    __syncthreads();
+    const Meta& lm = meta[(n_local - 1) % kMetaSlots];
+    if (lm.valid) {
+        if (tid == 0) {
+            ticket = atom_add_acq_rel(&ws.counters[(size_t)lm.proj * p.cap + lm.u.wseg], 1u);
+            *s_fold = (ticket == (unsigned)(lm.n_chunks - 1)) ? 1 : 0;
+        }
+        __syncthreads();
+        if (*s_fold == 1) shrink_fold<T>(p, ws, lm, tid);
+    }
+    cp_async_wait<0>();
+}
+
+// =============================================================================================
+// expand
+// =============================================================================================
+// Shared tile of B: JC rows x r_pad columns (row pitch r_pad*2 bytes = CPR 16-byte chunks).
+// With RPL = 8 / CPR rows per 128-byte line, chunk c of row j sits in line j / RPL at slot
+// (j % RPL) * CPR + (c ^ ((j / RPL) % CPR)): any 8 consecutive rows hit 8 different slots.
+__device__ __forceinline__ int b_tile_off(int row, int c, int cpr, int cpr_shift) {
+    const int rpl_shift = 3 - cpr_shift;
+    const int line = row >> rpl_shift;
+    const int slot = ((row & ((1 << rpl_shift) - 1)) << cpr_shift) + (c ^ (line & (cpr - 1)));
+    return line * 128 + slot * 16;
+}
+
+template <typename T>
+__device__ __forceinline__ void expand_issue(const ApplyParams& p, const WorkspaceView& ws, const Meta& m,
+                                             unsigned char* stage, int tid) {
+    if (!m.valid) return;
+    const ProjArgs& pj = p.proj[m.proj];
+    const int r = m.u.rank, r_pad = pad_rank(r);
+    const int jc = kSuper / n_sub(r_pad);                 // 1024, 1024, 512, 256 rows
+    const int cpr = r_pad / 8, cpr_shift = 31 - __clz(cpr);
+    const int pitch = b_pitch(p, r);
+    const T* B = reinterpret_cast<const T*>(pj.wb) + block_row0(p, m.u) * (long long)pj.h_out +
+                 (long long)m.c0 * pitch;
+    const unsigned wbase = smem_u32(stage);
+    {
+        const int c = tid & (cpr - 1), row0 = tid >> cpr_shift, rstep = kCtaThreads >> cpr_shift;
+        int nb = (r - c * 8) * 2;
+        nb = nb > 16 ? 16 : (nb < 0 ? 0 : nb);
+        const int rows_ok = pj.h_out - m.c0;              // rows of this unit inside the projection
+        for (int row = row0; row < jc; row += rstep) {
+            const int nbytes = row < rows_ok ? nb : 0;
+            const T* src = nbytes ? B + row * pitch + c * 8 : reinterpret_cast<const T*>(pj.wb);
+            cp_async16(wbase + b_tile_off(row, c, cpr, cpr_shift), src, nbytes);
         }
     }
-    if (threadIdx.x == 0) {
-        unsigned d = atomicAdd(&ws.ctl->done[0], 1u);
-        if (d == gridDim.x - 1) { ws.ctl->ticket[0] = 0u; ws.ctl->done[0] = 0u; }
+    // y tile (16-bit outputs only): ntok rows x jc columns
+    if (!p.y_f32) {
+        const unsigned ybase = wbase + kWBytes;
+        const int ypitch = jc * 2 + kYPitchPad;
+        const int cpt = jc / 8, cpt_shift = 31 - __clz(cpt);
+        const int c = tid & (cpt - 1), row0 = tid >> cpt_shift, rstep = kCtaThreads >> cpt_shift;
+        const bool ok = (m.c0 + c * 8) < pj.h_out;
+        const T* Y = reinterpret_cast<const T*>(pj.y) + m.c0 + c * 8;
+        for (int row = row0; row < m.u.ntok; row += rstep) {
+            const T* src = ok ? Y + (long long)m.u.tok[row] * pj.ldy : reinterpret_cast<const T*>(pj.y);
+            cp_async16(ybase + row * ypitch + c * 16, src, ok ? 16 : 0);
+        }
+    }
+    // v tile: ntok rows x r_pad floats
+    const unsigned vbase = wbase + kWBytes + kYBytes;
+    const int vpt = r_pad / 4, vpt_shift = 31 - __clz(vpt);
+    const int vt = m.u.ntok * vpt;
+    if (tid < vt) {
+        const int row = tid >> vpt_shift, c = tid & (vpt - 1);
+        const float* src = ws.v + ((size_t)m.proj * p.cap + m.u.start + row) * kMaxRank + c * 4;
+        cp_async16(vbase + row * (kVPitch * 4) + c * 16, src, 16);
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// expand: one unit = JC rows x r columns of B_a, JC = 16384 / r_pad
-// ---------------------------------------------------------------------------------------------
-template <typename T, int G>
-__device__ void expand_item(const ApplyParams& p, const PlanView& pv, const WorkspaceView& ws, const Item it,
-                            float* stage) {
-    constexpr int RL = kCtaThreads / G;          // rows covered by one CTA-wide load
-    constexpr int RLP = RL + 4;                  // padded pitch of one load's rows in the staging tile
-    constexpr int JC = kSlots * RL;
-    constexpr int JCP = kSlots * RLP;
-    constexpr int NV = kSlots * kTokTile;        // 32
-    constexpr int NKEEP = NV / G;                // values a lane keeps after the reduce
-    const ProjArgs& pj = p.proj[it.proj];
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int j0 = it.super * kSuper + it.sub * JC;
-    if (j0 >= pj.h_out) return;
-    const int a = pv.seg_adapter[it.seg];
-    const int r = pv.seg_rank[it.seg];
-    const int b = pv.seg_start[it.seg], e = pv.seg_start[it.seg + 1];
-    const int pitch = b_pitch(p, r);
-    const T* B = reinterpret_cast<const T*>(pj.wb) + block_row0(p, a, r) * (long long)pj.h_out;
-    const int g = tid % G, k0 = g * 8, row_in_load = tid / G;
-    const float scale = p.scalings ? p.scalings[a] : p.scale;
+// Tokens are the M rows of the MMA (rows 8..15 zero), 8 output rows of B the N columns: each
+// thread owns two adjacent outputs of one token and updates them in the shared y tile.
+template <typename T>
+__device__ __forceinline__ void expand_compute(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid) {
+    if (!m.valid) return;
+    const ProjArgs& pj = p.proj[m.proj];
+    const int lane = tid & 31, warp = tid >> 5;
+    const int r_pad = pad_rank(m.u.rank);
+    const int jc = kSuper / n_sub(r_pad);
+    const int cpr = r_pad / 8, cpr_shift = 31 - __clz(cpr);
+    const int KS = r_pad <= 16 ? 1 : r_pad / 16;          // k16 steps
+    const unsigned wbase = smem_u32(stage);
+    const float* vt = reinterpret_cast<const float*>(stage + kWBytes + kYBytes);
+    const int g = lane >> 2, t = lane & 3;
+    const int ntok = m.u.ntok;
+    const float scale = m.u.scale;
 
-    uint4 w[kSlots];
+    // A fragments: the fp32 intermediate of token g as a hi + lo pair of 16-bit values
+    unsigned ah[4][2], al[4][2];
 #pragma unroll
-    for (int q = 0; q < kSlots; ++q) {
-        const int row = j0 + q * RL + row_in_load;
-        w[q] = (row < pj.h_out && k0 < r) ? mask_lanes(ldg_nc16(B + (long long)row * pitch + k0), r - k0) : zero4();
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float v0 = 0.f, v1 = 0.f;
+            const int k = ks * 16 + h * 8 + 2 * t;
+            if (ks < KS && k < r_pad && g < ntok) {
+                const float2 vv = *reinterpret_cast<const float2*>(vt + g * kVPitch + k);
+                v0 = vv.x; v1 = vv.y;
+            }
+            const float h0 = Cvt<T>::round1(v0), h1 = Cvt<T>::round1(v1);
+            ah[ks][h] = Cvt<T>::pack2(h0, h1);
+            al[ks][h] = Cvt<T>::pack2(v0 - h0, v1 - h1);
+        }
     }
 
-    for (int pos0 = b; pos0 < e; pos0 += kTokTile) {
-        const int nt = min(kTokTile, e - pos0);
-        float vf[kTokTile][8];
+    const int NBW = jc / 8 / kWarps;                       // 8-row blocks per warp: 8, 8, 4, 2
+    const int jbase = warp * NBW * 8;
+    const int l7 = lane & 7, mi = lane >> 3;
+    unsigned char* ysb = stage + kWBytes;
+    const int ypitch = jc * 2 + kYPitchPad;
+    const int group = cpr == 1 ? 4 : 2;                    // blocks fetched by one ldmatrix.x4
+    for (int nb0 = 0; nb0 < NBW; nb0 += group) {
+        float acc[4][4];
 #pragma unroll
-        for (int tt = 0; tt < kTokTile; ++tt) {
-            if (tt < nt) {
-                const float4* vp = reinterpret_cast<const float4*>(
-                    &ws.v[((size_t)it.proj * p.cap + pos0 + tt) * kMaxRank + k0]);
-                float4 v0 = vp[0], v1 = vp[1];
-                vf[tt][0] = v0.x; vf[tt][1] = v0.y; vf[tt][2] = v0.z; vf[tt][3] = v0.w;
-                vf[tt][4] = v1.x; vf[tt][5] = v1.y; vf[tt][6] = v1.z; vf[tt][7] = v1.w;
-            } else {
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) vf[tt][j] = 0.f;
-            }
-        }
-        float acc[NV];
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        if (cpr == 1) {
+            const int row = jbase + (nb0 + mi) * 8 + l7;
+            unsigned b0, b1, b2, b3;
+            ldmatrix_x4(wbase + b_tile_off(row, 0, 1, 0), b0, b1, b2, b3);
+            Mma<T>::run(acc[0], ah[0][0], 0u, ah[0][1], 0u, b0, 0u);
+            Mma<T>::run(acc[0], al[0][0], 0u, al[0][1], 0u, b0, 0u);
+            Mma<T>::run(acc[1], ah[0][0], 0u, ah[0][1], 0u, b1, 0u);
+            Mma<T>::run(acc[1], al[0][0], 0u, al[0][1], 0u, b1, 0u);
+            Mma<T>::run(acc[2], ah[0][0], 0u, ah[0][1], 0u, b2, 0u);
+            Mma<T>::run(acc[2], al[0][0], 0u, al[0][1], 0u, b2, 0u);
+            Mma<T>::run(acc[3], ah[0][0], 0u, ah[0][1], 0u, b3, 0u);
+            Mma<T>::run(acc[3], al[0][0], 0u, al[0][1], 0u, b3, 0u);
+        } else {
+            const int row = jbase + (nb0 + (mi >> 1)) * 8 + l7;
 #pragma unroll
-        for (int q = 0; q < kSlots; ++q) {
-            float wf[8];
-            Cvt<T>::unpack8(w[q], wf);
-#pragma unroll
-            for (int tt = 0; tt < kTokTile; ++tt) {
-                float s = 0.f;
-                if (tt < nt) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) s = fmaf(wf[j], vf[tt][j], s);
-                }
-                acc[q * kTokTile + tt] = s;
-            }
-        }
-        halving_reduce<NV, G>(acc, lane);
-        // lane g keeps value indices [g*NKEEP, (g+1)*NKEEP): vi = q * kTokTile + tt
-#pragma unroll
-        for (int i = 0; i < NKEEP; ++i) {
-            const int vi = g * NKEEP + i;
-            const int q = vi / kTokTile, tt = vi % kTokTile;
-            stage[tt * JCP + q * RLP + row_in_load] = scale * acc[i];
-        }
-        __syncthreads();
-        // coalesced read-modify-write of y, 8 outputs per thread
-        const int chunks = JC / 8;
-        for (int idx = tid; idx < nt * chunks; idx += kCtaThreads) {
-            const int tt = idx / chunks, j8 = (idx % chunks) * 8;
-            const int col = j0 + j8;
-            if (col < pj.h_out) {
-                const int tok = pv.perm[pos0 + tt];
-                const float4* sp = reinterpret_cast<const float4*>(&stage[tt * JCP + (j8 / RL) * RLP + (j8 % RL)]);
-                const float4 s0 = sp[0], s1 = sp[1];
-                const float st[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-                if (p.y_f32) {
-                    float4* yp = reinterpret_cast<float4*>(reinterpret_cast<float*>(pj.y) + (long long)tok * pj.ldy + col);
-                    float4 y0 = yp[0], y1 = yp[1];
-                    y0.x += st[0]; y0.y += st[1]; y0.z += st[2]; y0.w += st[3];
-                    y1.x += st[4]; y1.y += st[5]; y1.z += st[6]; y1.w += st[7];
-                    yp[0] = y0; yp[1] = y1;
-                } else {
-                    uint4* yp = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)tok * pj.ldy + col);
-                    uint4 yv = *yp;
-                    float yf[8];
-                    Cvt<T>::unpack8(yv, yf);
-                    yv.x = Cvt<T>::pack2(yf[0] + st[0], yf[1] + st[1]);
-                    yv.y = Cvt<T>::pack2(yf[2] + st[2], yf[3] + st[3]);
-                    yv.z = Cvt<T>::pack2(yf[4] + st[4], yf[5] + st[5]);
-                    yv.w = Cvt<T>::pack2(yf[6] + st[6], yf[7] + st[7]);
-                    *yp = yv;
+            for (int ks = 0; ks < 4; ++ks) {
+                if (ks < KS) {
+                    unsigned b0, b1, b2, b3;
+                    ldmatrix_x4(wbase + b_tile_off(row, 2 * ks + (mi & 1), cpr, cpr_shift), b0, b1, b2, b3);
+                    Mma<T>::run(acc[0], ah[ks][0], 0u, ah[ks][1], 0u, b0, b1);
+                    Mma<T>::run(acc[0], al[ks][0], 0u, al[ks][1], 0u, b0, b1);
+                    Mma<T>::run(acc[1], ah[ks][0], 0u, ah[ks][1], 0u, b2, b3);
+                    Mma<T>::run(acc[1], al[ks][0], 0u, al[ks][1], 0u, b2, b3);
                 }
             }
         }
-        __syncthreads();
+        // y[token g][j, j+1] += scale * acc
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (i < group) {
+                const int j = jbase + (nb0 + i) * 8 + 2 * t;
+                if (g < ntok && m.c0 + j < pj.h_out) {
+                    const float d0 = scale * acc[i][0], d1 = scale * acc[i][1];
+                    if (p.y_f32) {
+                        float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) +
+                                                               (long long)m.u.tok[g] * pj.ldy + m.c0 + j);
+                        float2 yv = *yp;
+                        yv.x += d0; yv.y += d1;
+                        *yp = yv;
+                    } else {
+                        unsigned* yp = reinterpret_cast<unsigned*>(ysb + g * ypitch + j * 2);
+                        const unsigned w = *yp;
+                        float lo, hi;
+                        if (sizeof(T) == 2 && Cvt<T>::is_bf16) {
+                            lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xffff0000u);
+                        } else {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+                            lo = f.x; hi = f.y;
+                        }
+                        *yp = Cvt<T>::pack2(lo + d0, hi + d1);
+                    }
+                }
+            }
+        }
+    }
+    if (p.y_f32) return;
+    __syncthreads();
+    // coalesced write-back of the updated y tile
+    const int cpt = jc / 8, cpt_shift = 31 - __clz(cpt);
+    const int c = tid & (cpt - 1), row0 = tid >> cpt_shift, rstep = kCtaThreads >> cpt_shift;
+    if (m.c0 + c * 8 < pj.h_out) {
+        for (int row = row0; row < ntok; row += rstep) {
+            const uint4 val = *reinterpret_cast<const uint4*>(ysb + row * ypitch + c * 16);
+            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + c * 8) = val;
+        }
     }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kCtaThreads, 2) bgmv_expand_kernel(const __grid_constant__ ApplyParams p) {
-    __shared__ int s_item;
-    __shared__ __align__(16) float stage[kTokTile * (kSuper + 4 * kSlots)];   // 32.5 KB
+__global__ void __launch_bounds__(kCtaThreads, 1) bgmv_expand_kernel(const __grid_constant__ ApplyParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* stages = smem;
+    Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kExpandStage);
+
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
     if (hdr.error || hdr.cap != p.cap) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_out;
-    while (true) {
-        if (threadIdx.x == 0) s_item = (int)atomicAdd(&ws.ctl->ticket[1], 1u);
-        __syncthreads();
-        const int it = s_item;
-        __syncthreads();
-        if (it >= n_items) break;
-        Item item = decode_item(p, pv, it, n_units, true);
-        const int rpad = pad_rank(pv.seg_rank[item.seg]);
-        switch (rpad) {
-            case 8:  expand_item<T, 1>(p, pv, ws, item, stage); break;
-            case 16: expand_item<T, 2>(p, pv, ws, item, stage); break;
-            case 32: expand_item<T, 4>(p, pv, ws, item, stage); break;
-            default: expand_item<T, 8>(p, pv, ws, item, stage); break;
-        }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int first = blockIdx.x, stride = gridDim.x;
+    if (first >= n_items) return;
+    const int n_local = (n_items - first + stride - 1) / stride;
+
+    if (warp < kStages && warp < n_local) {
+        int word, proj, super;
+        fetch_meta_regs(p, pv, first + warp * stride, n_units, true, lane, word, proj, super);
+        store_meta(p, &meta[warp % kMetaSlots], lane, word, proj, super, true);
     }
-    if (threadIdx.x == 0) {
-        unsigned d = atomicAdd(&ws.ctl->done[1], 1u);
-        if (d == gridDim.x - 1) { ws.ctl->ticket[1] = 0u; ws.ctl->done[1] = 0u; }
+    __syncthreads();
+    for (int n = 0; n < kStages - 1; ++n) {
+        if (n < n_local) expand_issue<T>(p, ws, meta[n % kMetaSlots], stages + (n % kStages) * kExpandStage, tid);
+        cp_async_commit();
     }
+    for (int n = 0; n < n_local; ++n) {
+        const int nn = n + kStages - 1;
+        if (nn < n_local) expand_issue<T>(p, ws, meta[nn % kMetaSlots], stages + (nn % kStages) * kExpandStage, tid);
+        cp_async_commit();
+        int word = 0, mproj = 0, msuper = 0;
+        const int nm = n + kStages;
+        if (warp == 0 && nm < n_local) fetch_meta_regs(p, pv, first + nm * stride, n_units, true, lane, word, mproj, msuper);
+        cp_async_wait<kStages - 1>();
+        __syncthreads();
+        expand_compute<T>(p, meta[n % kMetaSlots], stages + (n % kStages) * kExpandStage, tid);
+        if (warp == 0 && nm < n_local) store_meta(p, &meta[nm % kMetaSlots], lane, word, mproj, msuper, true);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+}
+
+constexpr int kShrinkSmem = kStages * kShrinkStage + kRedBytes + kMetaSlots * (int)sizeof(Meta) + 16;
+constexpr int kExpandSmem = kStages * kExpandStage + kMetaSlots * (int)sizeof(Meta) + 16;
+
+template <typename T>
+cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(bgmv_shrink_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kShrinkSmem);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(bgmv_expand_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpandSmem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    if (!(p.flags & B200_LORA_ONLY_EXPAND)) bgmv_shrink_kernel<T><<<n_sm, kCtaThreads, kShrinkSmem, s>>>(p);
+    if (!(p.flags & B200_LORA_ONLY_SHRINK)) bgmv_expand_kernel<T><<<n_sm, kCtaThreads, kExpandSmem, s>>>(p);
+    return cudaGetLastError();
 }
 
 }  // namespace
 
 cudaError_t launch_bgmv(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s) {
-    const int grid = n_sm * 2;
-    const bool do_shrink = !(p.flags & B200_LORA_ONLY_EXPAND);
-    const bool do_expand = !(p.flags & B200_LORA_ONLY_SHRINK);
-    if (io_dtype == B200_LORA_F16) {
-        if (do_shrink) bgmv_shrink_kernel<__half><<<grid, kCtaThreads, 0, s>>>(p);
-        if (do_expand) bgmv_expand_kernel<__half><<<grid, kCtaThreads, 0, s>>>(p);
-    } else {
-        if (do_shrink) bgmv_shrink_kernel<__nv_bfloat16><<<grid, kCtaThreads, 0, s>>>(p);
-        if (do_expand) bgmv_expand_kernel<__nv_bfloat16><<<grid, kCtaThreads, 0, s>>>(p);
-    }
-    return cudaGetLastError();
+    if (io_dtype == B200_LORA_F16) return launch_pair<__half>(p, n_sm, s);
+    return launch_pair<__nv_bfloat16>(p, n_sm, s);
 }
 
 }  // namespace b200lora

@@ -13,9 +13,8 @@ namespace b200lora {
 constexpr int kMaxRank = B200_LORA_MAX_RANK;   // 64
 constexpr int kMaxProj = B200_LORA_MAX_PROJ;   // 4
 constexpr int kSuper = 2048;                   // columns (shrink) / rows (expand) per super-chunk
-constexpr int kCtaThreads = 256;
-constexpr int kSlots = 8;                      // 128-bit loads each thread keeps in flight
-constexpr int kTokTile = 4;                    // tokens per register pass
+constexpr int kCtaThreads = 512;
+constexpr int kChunkTok = 8;                   // BGMV work segments hold at most this many tokens
 constexpr int kTallMin = 32;                   // a contiguous segment at least this long is "tall"
 constexpr int kTileM = 128;                    // token rows of one tensor-core tile
 
@@ -25,15 +24,31 @@ struct PlanHeader {
     int n_tokens;
     int n_segs;
     int n_units;      // sum over short segments of r_pad/8
-    int error;        // 0 ok, 1 adapter id out of range, 2 bad segment table
+    int error;        // 0 ok, 1 adapter id out of range, 2 bad segment table, 3 rank promise broken
     int n_tiles;      // 128-row tiles of tall segments
     int cap;
     int n_adapters;
     int identity;     // 1: perm is the identity (rows pre-grouped)
     int n_units_short;  // units of short segments; they come first in unit_tab
-    int pad[7];
+    int n_wsegs;        // work segments
+    int pad[6];
 };
 static_assert(sizeof(PlanHeader) == 64, "plan header is 16 words");
+
+// One BGMV work unit: a work segment (<= 8 tokens of one adapter) times one sub-range of
+// columns (shrink) or rows (expand).  Everything a CTA needs to start loading, in 64 bytes.
+struct UnitRec {
+    int adapter;
+    int rank;
+    short sub;        // index of the sub-range inside a 2048-wide super-chunk
+    short ntok;
+    float scale;      // the adapter's scaling
+    int wseg;         // work-segment index (selects the split-K arrival counter)
+    int start;        // sorted position of the first token
+    int cum_lo, cum_hi;   // cum_ranks[adapter] (packed pools)
+    int tok[8];       // token rows
+};
+static_assert(sizeof(UnitRec) == 64, "unit record is 16 words");
 
 struct PlanView {
     PlanHeader* hdr;
@@ -42,7 +57,10 @@ struct PlanView {
     int* seg_adapter;   // [cap]
     int* seg_rank;      // [cap]       rank of the segment's adapter
     int* seg_flags;     // [cap]       bit0: tall (handled by the tensor-core tiles)
-    int* unit_tab;      // [8 * cap]   (seg << 3) | sub
+    int* ws_start;      // [cap + 1]   work segments: adapter segments cut into <= kChunkTok tokens
+    int* ws_adapter;    // [cap]
+    int* ws_rank;       // [cap]
+    int* unit_tab;      // [8 * cap][16]  one record per 32 KB weight unit (see UnitRec)
     int* tile_tab;      // [cap]       (seg << 12) | m-tile, for tall segments (cap/kTallMin used)
     int* hist;          // [n_adapters + 1]
 };
@@ -50,7 +68,7 @@ struct PlanView {
 __host__ __device__ inline size_t plan_words(int cap, int n_adapters) {
     // header + perm + seg_start + 3 seg arrays + units + tiles + hist, each padded to 4 words
     auto pad4 = [](size_t w) { return (w + 3) & ~size_t(3); };
-    return 16 + pad4(cap) + pad4(cap + 1) + 3 * pad4(cap) + pad4(8 * (size_t)cap) + pad4(cap) +
+    return 16 + pad4(cap) + 2 * pad4(cap + 1) + 5 * pad4(cap) + 16 * 8 * (size_t)cap + pad4(cap) +
            pad4((size_t)n_adapters + 1);
 }
 
@@ -64,7 +82,10 @@ __host__ __device__ inline PlanView plan_view(void* base, int cap, int n_adapter
     v.seg_adapter = w;                             w += pad4(cap);
     v.seg_rank = w;                                w += pad4(cap);
     v.seg_flags = w;                               w += pad4(cap);
-    v.unit_tab = w;                                w += pad4(8 * (size_t)cap);
+    v.ws_start = w;                                w += pad4(cap + 1);
+    v.ws_adapter = w;                              w += pad4(cap);
+    v.ws_rank = w;                                 w += pad4(cap);
+    v.unit_tab = w;                                w += 16 * 8 * (size_t)cap;
     v.tile_tab = w;                                w += pad4(cap);
     v.hist = w;
     (void)n_adapters;
@@ -144,13 +165,21 @@ __device__ __forceinline__ long long block_row0(const ApplyParams& p, int a, int
     if (p.packed) return (long long)p.n_layers * p.cum_ranks[a] + (long long)p.layer * r;
     return ((long long)a * p.n_layers + p.layer) * p.r_pool;
 }
+__device__ __forceinline__ long long block_row0(const ApplyParams& p, const UnitRec& u) {
+    if (p.packed)
+        return (long long)p.n_layers * (((long long)u.cum_hi << 32) | (unsigned)u.cum_lo) + (long long)p.layer * u.rank;
+    return ((long long)u.adapter * p.n_layers + p.layer) * p.r_pool;
+}
 __device__ __forceinline__ int b_pitch(const ApplyParams& p, int r) { return p.packed ? r : p.r_pool; }
 
-__device__ __forceinline__ int pad_rank(int r) { return r <= 8 ? 8 : r <= 16 ? 16 : r <= 32 ? 32 : 64; }
+__host__ __device__ __forceinline__ int pad_rank(int r) { return r <= 8 ? 8 : r <= 16 ? 16 : r <= 32 ? 32 : 64; }
+// sub-ranges per 2048-wide super-chunk for a padded rank: 8->2, 16->2, 32->4, 64->8
+__host__ __device__ __forceinline__ int n_sub(int r_pad) { return r_pad <= 16 ? 2 : r_pad / 8; }
 
 // ---- 16-bit -> fp32 helpers ------------------------------------------------------------------
 template <typename T> struct Cvt;
 template <> struct Cvt<__half> {
+    static constexpr bool is_bf16 = false;
     static __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
         const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
@@ -163,6 +192,7 @@ template <> struct Cvt<__half> {
     static __device__ __forceinline__ float round1(float a) { return __half2float(__float2half_rn(a)); }
 };
 template <> struct Cvt<__nv_bfloat16> {
+    static constexpr bool is_bf16 = true;
     static __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
         const unsigned* w = reinterpret_cast<const unsigned*>(&u);
 #pragma unroll
@@ -184,12 +214,21 @@ __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
 __device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // ---- launchers implemented by the kernel files ---------------------------------------------
+struct PlanAdapters {          // what the plan bakes into its unit records
+    const int* ranks;
+    const long long* cum_ranks;   // NULL for dense pools
+    const float* scalings;        // NULL: uniform `scale`
+    float scale;
+    int r_pool;
+    int n_adapters;
+    int ranks_pow2;               // caller's promise: every rank is 8/16/32/64 (dense: == r_pool)
+};
 cudaError_t launch_plan_build(void* plan, int cap, const void* ids, int ids_i64, int n_tokens,
-                              const int* ranks, int r_pool, int n_adapters, cudaStream_t s);
+                              const PlanAdapters& ad, cudaStream_t s);
 cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts, const int* seg_adapter,
-                                      int n_segs, int n_tokens, const int* ranks, int r_pool,
-                                      int n_adapters, cudaStream_t s);
+                                      int n_segs, int n_tokens, const PlanAdapters& ad, cudaStream_t s);
 cudaError_t launch_bgmv(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
+cudaError_t launch_bgmv_tma(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
 bool sgmv_tiles_supported(const ApplyParams& p);
 cudaError_t launch_sgmv_tiles(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
 

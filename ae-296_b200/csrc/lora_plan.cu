@@ -110,49 +110,77 @@ __device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* 
     __syncthreads();
 }
 
-// Phase B: classify segments, lay out units and tiles.
-__device__ void build_units(PlanView pv, const int* ranks, int r_pool, int* smem) {
+// Phase B: classify segments, cut them into work segments, lay out units and tiles.
+__device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
+    const int* ranks = ad.ranks;
+    const long long* cum_ranks = ad.cum_ranks;
+    const int r_pool = ad.r_pool;
     const int tid = threadIdx.x;
     int* warp_sums = smem;
     const int S = pv.hdr->n_segs;
     const bool identity = pv.hdr->identity != 0;
-    // pass 1: rank, tall flag; count units of short and of tall segments, and tiles
-    int tot_short = 0, tot_tall = 0, tot_tiles = 0;
+    // pass 0 totals the units of short segments (they are listed first); pass 1 writes
+    int tot_short = 0, tot_tall = 0, tot_tiles = 0, tot_ws = 0;
     for (int pass = 0; pass < 2; ++pass) {
-        int c_short = 0, c_tall = 0, c_tiles = 0;
+        int c_short = 0, c_tall = 0, c_tiles = 0, c_ws = 0;
         for (int base = 0; base < S; base += kPlanThreads) {
             int s = base + tid;
-            int us = 0, ut = 0, nt = 0, r = 0, tall = 0, len = 0;
+            int us = 0, ut = 0, nt = 0, r = 0, tall = 0, len = 0, nchunk = 0, b = 0, a = 0;
             if (s < S) {
-                int a = pv.seg_adapter[s];
+                a = pv.seg_adapter[s];
                 r = ranks ? ranks[a] : r_pool;
+                if (ad.ranks_pow2 && !((r == 8 || r == 16 || r == 32 || r == 64) && (cum_ranks || r == r_pool)))
+                    pv.hdr->error = 3;                  // the fast kernels were promised these ranks
                 if (r < 1) r = 1;
                 if (r > kMaxRank) r = kMaxRank;
-                int b = pv.seg_start[s], e = pv.seg_start[s + 1];
+                b = pv.seg_start[s];
+                int e = pv.seg_start[s + 1];
                 len = e - b;
                 bool contig = identity || (pv.perm[e - 1] - pv.perm[b] == len - 1);
                 tall = (len >= kTallMin && contig) ? 1 : 0;
-                int u = pad_rank(r) / 8;
+                nchunk = (len + kChunkTok - 1) / kChunkTok;
+                int u = nchunk * n_sub(pad_rank(r));
                 us = tall ? 0 : u;
                 ut = tall ? u : 0;
                 nt = tall ? (len + kTileM - 1) / kTileM : 0;
             }
-            int t0, t1, t2;
+            int t0, t1, t2, t3;
             int o_s = block_scan_excl(us, t0, warp_sums);
             int o_t = block_scan_excl(ut, t1, warp_sums);
             int o_m = block_scan_excl(nt, t2, warp_sums);
+            int o_w = block_scan_excl(nchunk, t3, warp_sums);
             if (pass == 1 && s < S) {
                 pv.seg_rank[s] = r;
                 pv.seg_flags[s] = tall;
                 int u0 = tall ? tot_short + c_tall + o_t : c_short + o_s;
-                for (int j = 0; j < us + ut; ++j) pv.unit_tab[u0 + j] = (s << 3) | j;
+                const int w0 = c_ws + o_w;
+                const int per = (len + nchunk - 1) / nchunk;         // balanced chunk length
+                const int nsub = n_sub(pad_rank(r));
+                const long long cum = cum_ranks ? cum_ranks[a] : 0;
+                for (int c = 0; c < nchunk; ++c) {
+                    const int cb = b + min(c * per, len), ce = b + min((c + 1) * per, len);
+                    pv.ws_start[w0 + c] = cb;
+                    pv.ws_adapter[w0 + c] = a;
+                    pv.ws_rank[w0 + c] = r;
+                    UnitRec rec;
+                    rec.adapter = a; rec.rank = r; rec.ntok = (short)(ce - cb); rec.wseg = w0 + c; rec.start = cb;
+                    rec.scale = ad.scalings ? ad.scalings[a] : ad.scale;
+                    rec.cum_lo = (int)(cum & 0xffffffffll); rec.cum_hi = (int)(cum >> 32);
+                    for (int i = 0; i < 8; ++i) rec.tok[i] = pv.perm[cb + min(i, ce - cb - 1)];
+                    for (int j = 0; j < nsub; ++j) {
+                        rec.sub = (short)j;
+                        reinterpret_cast<UnitRec*>(pv.unit_tab)[u0 + c * nsub + j] = rec;
+                    }
+                }
                 for (int m = 0; m < nt; ++m) pv.tile_tab[c_tiles + o_m + m] = (s << 12) | m;
             }
-            c_short += t0; c_tall += t1; c_tiles += t2;
+            c_short += t0; c_tall += t1; c_tiles += t2; c_ws += t3;
         }
-        tot_short = c_short; tot_tall = c_tall; tot_tiles = c_tiles;
+        tot_short = c_short; tot_tall = c_tall; tot_tiles = c_tiles; tot_ws = c_ws;
     }
     if (tid == 0) {
+        pv.ws_start[tot_ws] = pv.hdr->n_tokens;
+        pv.hdr->n_wsegs = tot_ws;
         pv.hdr->n_units = tot_short + tot_tall;
         pv.hdr->n_units_short = tot_short;
         pv.hdr->n_tiles = tot_tiles;
@@ -161,7 +189,8 @@ __device__ void build_units(PlanView pv, const int* ranks, int r_pool, int* smem
 
 template <typename IdT>
 __global__ void __launch_bounds__(kPlanThreads, 1)
-plan_build_kernel(void* plan, int cap, const void* ids, int T, const int* ranks, int r_pool, int N) {
+plan_build_kernel(void* plan, int cap, const void* ids, int T, const PlanAdapters ad) {
+    const int N = ad.n_adapters;
     __shared__ int smem[64];
     PlanView pv = plan_view(plan, cap, N);
     if (threadIdx.x == 0) {
@@ -172,12 +201,13 @@ plan_build_kernel(void* plan, int cap, const void* ids, int T, const int* ranks,
     build_from_ids<IdT>(pv, ids, T, N, smem);
     __syncthreads();
     if (pv.hdr->error) return;
-    build_units(pv, ranks, r_pool, smem);
+    build_units(pv, ad, smem);
 }
 
 __global__ void __launch_bounds__(kPlanThreads, 1)
 plan_segments_kernel(void* plan, int cap, const int* seg_starts, const int* seg_adapter, int S, int T,
-                     const int* ranks, int r_pool, int N) {
+                     const PlanAdapters ad) {
+    const int N = ad.n_adapters;
     __shared__ int smem[64];
     PlanView pv = plan_view(plan, cap, N);
     const int tid = threadIdx.x;
@@ -201,23 +231,21 @@ plan_segments_kernel(void* plan, int cap, const int* seg_starts, const int* seg_
     for (int t = tid; t < T; t += kPlanThreads) pv.perm[t] = t;
     if (tid == 0) { pv.seg_start[S] = T; pv.hdr->n_segs = S; pv.hdr->n_tokens = T; }
     __syncthreads();
-    build_units(pv, ranks, r_pool, smem);
+    build_units(pv, ad, smem);
 }
 
 cudaError_t launch_plan_build(void* plan, int cap, const void* ids, int ids_i64, int n_tokens,
-                              const int* ranks, int r_pool, int n_adapters, cudaStream_t s) {
+                              const PlanAdapters& ad, cudaStream_t s) {
     if (ids_i64)
-        plan_build_kernel<long long><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ranks, r_pool, n_adapters);
+        plan_build_kernel<long long><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ad);
     else
-        plan_build_kernel<int><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ranks, r_pool, n_adapters);
+        plan_build_kernel<int><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ad);
     return cudaGetLastError();
 }
 
 cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts, const int* seg_adapter,
-                                      int n_segs, int n_tokens, const int* ranks, int r_pool,
-                                      int n_adapters, cudaStream_t s) {
-    plan_segments_kernel<<<1, kPlanThreads, 0, s>>>(plan, cap, seg_starts, seg_adapter, n_segs, n_tokens,
-                                                    ranks, r_pool, n_adapters);
+                                      int n_segs, int n_tokens, const PlanAdapters& ad, cudaStream_t s) {
+    plan_segments_kernel<<<1, kPlanThreads, 0, s>>>(plan, cap, seg_starts, seg_adapter, n_segs, n_tokens, ad);
     return cudaGetLastError();
 }
 

@@ -34,17 +34,24 @@ def _require_cuda(*tensors):
 
 
 def _adapters_struct(n_adapters, n_layers, r_pool, ranks=None, scalings=None, cum_ranks=None,
-                     packed=False, scale=1.0) -> Adapters:
+                     packed=False, scale=1.0, ranks_pow2=False) -> Adapters:
     return Adapters(
         ranks.data_ptr() if ranks is not None else None,
         scalings.data_ptr() if scalings is not None else None,
         cum_ranks.data_ptr() if cum_ranks is not None else None,
-        n_adapters, n_layers, r_pool, 1 if packed else 0, float(scale))
+        n_adapters, n_layers, r_pool, 1 if packed else 0, float(scale), 1 if ranks_pow2 else 0)
 
 
 def adapters_of(pool: AdapterPool) -> Adapters:
+    """The pool's adapter table; promises power-of-two ranks to the library when the host
+    copy of the ranks shows it (which selects the TMA kernels)."""
+    rh = pool.ranks_host
+    if pool.packed:
+        pow2 = bool(np.isin(rh, (8, 16, 32, 64)).all())
+    else:
+        pow2 = bool((rh == pool.r_pool).all()) and pool.r_pool in (8, 16, 32, 64)
     return _adapters_struct(pool.n_adapters, pool.n_layers, pool.r_pool, pool.ranks, pool.scalings,
-                            pool.cum_ranks, pool.packed, 1.0)
+                            pool.cum_ranks, pool.packed, 1.0, pow2)
 
 
 class LoraPlan:
@@ -95,6 +102,11 @@ class LoraPlan:
 
 class LoraWorkspace:
     """Scratch for the ``[T, r]`` intermediate and the split-K partial sums."""
+
+    def check(self) -> None:
+        """Synchronises and raises if a kernel recorded a device-side error (expired wait)."""
+        check(_lib.lib().b200_lora_workspace_status(self.buf.data_ptr(), _stream(self.buf.device)),
+              "workspace_status")
 
     def __init__(self, max_tokens: int, n_proj: int, max_h_in: int, device="cuda"):
         self.max_tokens, self.n_proj, self.max_h_in = int(max_tokens), int(n_proj), int(max_h_in)

@@ -144,21 +144,30 @@ def main():
     batch = L.LoraBatch(T, wl.n_adapters, wl.projections[0].h_in, 3, dev)
     stream = torch.cuda.Stream(dev)
 
-    def one_pass(flags=0):
-        batch.set_ids(ids, pools["q"])
+    def one_pass(flags=0, plan=True):
+        if plan:
+            batch.set_ids(ids, pools["q"])
         for l in range(n_layers):
             batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l, flags)
             batch.apply([(x_o[l], ys["o"][l], pools["o"])], l, flags)
 
     launches_per_pass = 1 + n_layers * 4
 
-    def capture(flags=0):
+    def capture(flags=0, plan=True):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
-            one_pass(flags)
+            one_pass(flags, plan)
             stream.synchronize()
             with torch.cuda.graph(g, stream=stream):
-                one_pass(flags)
+                one_pass(flags, plan)
+        return g
+
+    def capture_plan_only():
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g, stream=stream):
+                for _ in range(8):
+                    batch.set_ids(ids, pools["q"])
         return g
 
     def timed(graph, steps, warmup):
@@ -199,8 +208,9 @@ def main():
     e = 2
     exp_bytes = sum(rsum * p.h_out * e + 2 * T * p.h_out * e for p in wl.projections) * n_layers
     shr_bytes = sum(rsum * p.h_in * e + T * p.h_in * e + 4 * T for p in wl.projections) * n_layers
-    ms_exp = timed(capture(_lib.ONLY_EXPAND), args.steps, 3)
-    ms_shr = timed(capture(_lib.ONLY_SHRINK), args.steps, 3)
+    ms_exp = timed(capture(_lib.ONLY_EXPAND, plan=False), args.steps, 3)
+    ms_shr = timed(capture(_lib.ONLY_SHRINK, plan=False), args.steps, 3)
+    us_plan = timed(capture_plan_only(), args.steps, 3) * 1e3 / 8
     n_exp_launch = n_layers * 2
     ach = exp_bytes / (ms_exp * 1e-3) / 1e9
     roofline = {
@@ -210,6 +220,7 @@ def main():
         "frac_of_8TBs_nominal": ach / 8000.0,
         "shrink": {"kernel": "bgmv_shrink_kernel", "achieved": shr_bytes / (ms_shr * 1e-3) / 1e9,
                    "frac": shr_bytes / (ms_shr * 1e-3) / 1e9 / peak, "us_per_launch": ms_shr * 1e3 / n_exp_launch},
+        "plan_us": us_plan,
         "whole_pass": {"bytes": wl.bytes_per_layer() * n_layers,
                        "achieved": wl.bytes_per_layer() * n_layers / (ms * 1e-3) / 1e9,
                        "frac": wl.bytes_per_layer() * n_layers / (ms * 1e-3) / 1e9 / peak},

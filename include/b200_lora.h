@@ -66,6 +66,10 @@ typedef struct b200_lora_adapters {
     int32_t r_pool;            /* R of the dense layout; upper bound of every rank */
     int32_t packed;            /* 0 dense, 1 packed */
     float   scale;
+    int32_t ranks_pow2;        /* caller's promise that every rank is 8, 16, 32 or 64 (and equals r_pool
+                                  when dense); selects the TMA kernels.  Checked on the device when a
+                                  plan is built: a broken promise yields B200_LORA_ERR_RANK from
+                                  b200_lora_plan_read and a plan that applies nothing. */
 } b200_lora_adapters;
 
 /* One projection (q, k, v or o): replaces one (x, pool pair, y) triple of
@@ -123,6 +127,10 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
                     const void* plan, int32_t max_tokens, int32_t layer, int32_t io_dtype,
                     int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes,
                     void* stream);
+
+/* Reads the workspace's sticky device-side error word (synchronises `stream`):
+ * B200_LORA_OK, or B200_LORA_ERR_TIMEOUT if a bounded wait inside a kernel expired. */
+int b200_lora_workspace_status(const void* workspace, void* stream);
 
 /* ---- the reference's operator call -------------------------------------------------------
  * Same arguments as punica.ops.add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx,

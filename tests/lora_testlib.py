@@ -60,6 +60,7 @@ class Case:
             batch.set_ids(self.ids_dev.to(ids_dtype), self.pool)
         batch.apply([(self.x, y, self.pool)], layer, flags)
         torch.cuda.synchronize()
+        batch.workspace.check()          # no bounded device-side wait expired
         return y
 
 
