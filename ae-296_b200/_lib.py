@@ -34,7 +34,7 @@ class LoraError(RuntimeError):
 class Adapters(C.Structure):
     _fields_ = [("ranks", C.c_void_p), ("scalings", C.c_void_p), ("cum_ranks", C.c_void_p),
                 ("n_adapters", C.c_int32), ("n_layers", C.c_int32), ("r_pool", C.c_int32),
-                ("packed", C.c_int32), ("scale", C.c_float), ("ranks_pow2", C.c_int32)]
+                ("packed", C.c_int32), ("scale", C.c_float), ("ranks_pow2", C.c_int32), ("total_rank", C.c_int64)]
 
 
 class Proj(C.Structure):

@@ -1,6 +1,8 @@
 // extern "C" entry points declared in include/b200_lora.h: argument checks and launches only.
 #include <string.h>
 
+#include <mutex>
+
 #include "lora_common.cuh"
 
 using namespace b200lora;
@@ -24,6 +26,64 @@ int sm_count() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+// ---- tensor maps for the TMA kernels --------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        tried = true;
+    }
+    return fn;
+}
+
+// 2-D map over a row-major 16-bit matrix [rows, inner]; cached per (base, inner, rows, box)
+bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner,
+                   uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    struct Entry { const void* base; uint64_t inner, rows; uint32_t bi, br; int sw; CUtensorMap map; };
+    static Entry cache[64];
+    static int n_cached = 0, next = 0;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < n_cached; ++i) {
+        const Entry& e = cache[i];
+        if (e.base == base && e.inner == inner && e.rows == rows && e.bi == box_inner && e.br == box_rows &&
+            e.sw == (int)swizzle) { *out = e.map; return true; }
+    }
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    alignas(64) CUtensorMap m;
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    Entry& e = cache[next];
+    e.base = base; e.inner = inner; e.rows = rows; e.bi = box_inner; e.br = box_rows; e.sw = (int)swizzle; e.map = m;
+    next = (next + 1) % 64;
+    if (n_cached < 64) ++n_cached;
+    *out = m;
+    return true;
+}
+
+// rows of an A pool viewed as a [rows, h_in] matrix
+uint64_t pool_rows(const b200_lora_adapters* ad) {
+    if (!ad->packed) return (uint64_t)ad->n_adapters * ad->n_layers * ad->r_pool;
+    if (ad->total_rank > 0) return (uint64_t)ad->total_rank * ad->n_layers;
+    return (uint64_t)ad->n_adapters * ad->n_layers * kMaxRank;       // upper bound
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -192,7 +252,12 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     if (!(p.flags & B200_LORA_NO_TENSOR)) e = launch_sgmv_tiles(p, io_dtype, n_sm, s);
     bool fast = fast_ranks(adapters);
     for (int i = 0; i < n_proj; ++i)
-        if ((projs[i].h_in % 256) || (projs[i].h_out % 256)) fast = false;
+        if ((projs[i].h_in % 256) || (projs[i].h_out % 256) || projs[i].h_in > 8192) fast = false;
+    if (fast) {
+        for (int i = 0; i < n_proj && fast; ++i)
+            fast = tensor_map_2d(&p.amap[i], projs[i].wa, (uint64_t)projs[i].h_in, pool_rows(adapters), 128, 8,
+                                 CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
     if (e == cudaSuccess) e = fast ? launch_bgmv_tma(p, io_dtype, n_sm, s) : launch_bgmv(p, io_dtype, n_sm, s);
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }

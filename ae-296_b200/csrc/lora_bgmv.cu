@@ -2,7 +2,7 @@
 // segments of at most 8 tokens.
 //
 // Both kernels are HBM-bound weight streamers built the same way: one persistent CTA per SM
-// walks 32 KB weight units through a 4-stage shared-memory ring filled with 128-bit cp.async
+// walks <= 16 KB weight units through a 6-stage shared-memory ring filled with 128-bit cp.async
 // loads (weights, the unit's activation rows, and for the expand the y tile it will update),
 // so ~100 KB of loads per SM are in flight while earlier units are being computed.  Tiles are
 // XOR-swizzled at 16-byte granularity so ldmatrix reads are conflict-free, and the arithmetic
@@ -24,12 +24,12 @@ namespace b200lora {
 
 namespace {
 
-constexpr int kStages = 4;
-constexpr int kMetaSlots = 8;
-constexpr int kWBytes = 32768;                 // weights of one unit
-constexpr int kXBytes = 16384;                 // shrink: 8 tokens x <= 1024 columns
+constexpr int kStages = 6;
+constexpr int kMetaSlots = 16;
+constexpr int kWBytes = 16384;                 // weights of one unit (rank 8 pads to 16 rows)
+constexpr int kXBytes = 8192;                  // shrink: 8 tokens x <= 512 columns
 constexpr int kYPitchPad = 16;                 // bytes added to a y-tile row against bank conflicts
-constexpr int kYBytes = 8 * (1024 * 2 + kYPitchPad);
+constexpr int kYBytes = 8 * (512 * 2 + kYPitchPad);
 constexpr int kVPitch = 72;                    // floats per token row of the v tile
 constexpr int kVBytes = 8 * kVPitch * 4;
 constexpr int kShrinkStage = kWBytes + kXBytes;
@@ -470,7 +470,7 @@ __device__ __forceinline__ void expand_compute(const ApplyParams& p, const Meta&
         for (int i = 0; i < 4; ++i) {
             if (i < group) {
                 const int j = jbase + (nb0 + i) * 8 + 2 * t;
-                if (g < ntok && m.c0 + j < pj.h_out) {
+                if (nb0 + i < NBW && g < ntok && m.c0 + j < pj.h_out) {
                     const float d0 = scale * acc[i][0], d1 = scale * acc[i][1];
                     if (p.y_f32) {
                         float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) +

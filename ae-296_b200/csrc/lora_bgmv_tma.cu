@@ -1,18 +1,29 @@
-// Decode BGMV, fast path: TMA bulk copies + mbarrier pipeline + mma.sync.
+// Decode BGMV, fast path: TMA copies + mbarrier pipeline + mma.sync.
 //
-// Used when every adapter rank is 8, 16, 32 or 64 and every projection width is a multiple
-// of 256, which makes each unit's weight tile a handful of plain contiguous byte ranges:
-//   shrink  A rows [r, KC] of one adapter/layer     -> r bulk copies (one per row)
-//   expand  B rows [JC, r] of one adapter/layer     -> ONE bulk copy (rows are contiguous)
-// A dedicated producer warp walks the unit list and issues `cp.async.bulk` copies (weights,
-// the unit's activation rows, the y tile to update) into a 4-stage shared-memory ring; each
-// stage's arrival is tracked by an mbarrier transaction count.  The consumer warps never
-// compute a load address: they wait on the stage's barrier, read MMA fragments with 128-bit
-// shared loads and run mma.sync m16n8k16 with the unit's <= 8 tokens as M rows, weight rows
-// as N, fp32 accumulators.  Tiles are stored unswizzled; the k index inside a 32-wide block
-// is permuted identically for both operands so that each thread's fragment is one contiguous
-// 16-byte chunk, and rows are padded by 64 bytes (shrink) so those reads are conflict-free.
-// The expand updates a staged y tile in shared memory and writes it back with bulk stores.
+// Used when every adapter rank is 8, 16, 32 or 64 and every projection width is a multiple of
+// 256.  A CTA is two producer warps plus eight consumer warps around a 4-stage shared-memory
+// ring; two CTAs share an SM, so ~100 KB of loads per SM are in flight.  The producers walk a
+// contiguous range of <= 16 KB weight units (alternate units each) and fill a stage with ONE instruction per kind:
+//   shrink  A rows [r, KC]   -> up to eight [8 x 128] boxes of a 2-D tensor map over the A pool
+//           x rows [ntok, KC]-> one bulk copy per token
+//   expand  B rows [JC, r]   -> one contiguous bulk copy; plus one copy per token for the y
+//           tile that will be updated and for the fp32 intermediate
+// Each stage's arrival is tracked by an mbarrier transaction count; consumers never compute a
+// load address.  They read MMA fragments with 128-bit shared loads (tiles are stored
+// unswizzled; the k index inside a 32-wide block is permuted identically for both operands so
+// that a thread's fragment is one contiguous 16-byte chunk) and run mma.sync m16n8k16 with
+// fp32 accumulators.  The legacy MMA path of this part has a long dependent-issue latency, so
+// every warp keeps several independent accumulators in flight.
+//
+// shrink: weight rows are the M rows, the unit's <= 8 tokens the N columns.  Consecutive units
+// of one (projection, work segment) are accumulated in registers; when the run ends the CTA
+// publishes ONE split-K partial, marks its slot in a bit mask and adds the run length to an
+// arrival counter.  The CTA that completes the count folds the marked slots in ascending
+// order, so results are bit-reproducible.
+// expand: tokens are the M rows - rows 0..7 carry the hi halves of the fp32 intermediate, rows
+// 8..15 the lo halves, so one MMA yields both products - and 8 output rows of B are the N
+// columns; results are added into the staged y tile, which is written back with coalesced
+// 16-byte stores.
 //
 // Every mbarrier wait is bounded: on expiry the thread records an error word in the workspace
 // and carries on with the same control flow, so the kernel always terminates.
@@ -21,28 +32,46 @@
 // reference (lightllm/models/lora_gpu.py:138,150,162), pools as at :33-40.
 #include "lora_common.cuh"
 
+// Optional cycle accounting for tuning (-DB200_LORA_TRACE): CTA 0 adds the cycles its producer
+// lane and its first consumer thread spend in each phase to workspace pad words.
+#ifdef B200_LORA_TRACE
+#define TRACE_DECL long long tr_t0 = clock64(); long long tr_acc[6] = {0, 0, 0, 0, 0, 0};
+#define TRACE_MARK(i) { long long tr_t1 = clock64(); tr_acc[i] += tr_t1 - tr_t0; tr_t0 = tr_t1; }
+#define TRACE_FLUSH(cond, base) if ((cond) && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) atomicAdd(&ws.ctl->pad[(base) + i], (unsigned)(tr_acc[i] >> 4)); }
+#else
+#define TRACE_DECL
+#define TRACE_MARK(i)
+#define TRACE_FLUSH(cond, base)
+#endif
+
 namespace b200lora {
 
 namespace {
 
 constexpr int kStages = 4;
-constexpr int kConsWarps = 16;
+constexpr int kMetaSlots = 2 * kStages;
+constexpr int kConsWarps = 8;
 constexpr int kConsThreads = kConsWarps * 32;
-constexpr int kThreads = kConsThreads + 32;       // + one producer warp
-constexpr int kRowPad = 64;                       // bytes added to shrink tile rows
-constexpr int kShrinkStage = 50688;               // max over rank classes of W + X tiles
+constexpr int kProdWarps = 2;                     // producer warps take alternate items
+constexpr int kThreads = kConsThreads + kProdWarps * 32;
+constexpr int kCtasPerSm = 2;
+constexpr int kBoxCols = 128, kBoxRows = 8;       // shrink weight box: 2 KB
+constexpr int kBoxBytes = kBoxCols * kBoxRows * 2;
+constexpr int kWTile = 16384;                     // weight tile of one unit
+constexpr int kXPad = 64;                         // bytes added to an x-tile row (bank spread)
+constexpr int kXBytes = 8 * (512 * 2 + kXPad);
+constexpr int kShrinkStage = kWTile + kXBytes;
 constexpr int kYPad = 16;
-constexpr int kYBytes = 8 * (1024 * 2 + kYPad);
+constexpr int kYBytes = 8 * (512 * 2 + kYPad);
 constexpr int kVPitch = 72;                       // floats per token row of the v tile
 constexpr int kVBytes = 8 * kVPitch * 4;
-constexpr int kExpandStage = 32768 + kYBytes + kVBytes;
-constexpr int kRedBytes = 8 * 8 * 68 * 4;
+constexpr int kExpandStage = kWTile + kYBytes + kVBytes;
+constexpr int kRedBytes = 8 * 8 * 20 * 4;         // cross-warp reduction tile (largest: rank 16, 8 slices)
 constexpr unsigned kSpinLimit = 1u << 22;
 
 struct Meta {
     UnitRec u;
-    int proj, c0, valid, kc, n_chunks;
-    int width_ok;           // columns (shrink) / rows (expand) of the unit inside the projection
+    int proj, c0, valid, kc, n_chunks, width_ok;
     int pad[2];
 };
 static_assert(sizeof(Meta) == 96, "meta slot");
@@ -79,29 +108,27 @@ __device__ __forceinline__ void bulk_g2s(unsigned dst, const void* src, unsigned
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void bulk_s2g(void* dst, unsigned src, unsigned bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes)
-                 : "memory");
+__device__ __forceinline__ void tensor_g2s_2d(unsigned dst, const void* tmap, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsThreads) : "memory"); }
 
 template <typename T> struct Mma;
 template <> struct Mma<__half> {
-    static __device__ __forceinline__ void run(float (&c)[4], unsigned a0, unsigned a2, unsigned b0, unsigned b1) {
+    static __device__ __forceinline__ void run(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
         asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     }
 };
 template <> struct Mma<__nv_bfloat16> {
-    static __device__ __forceinline__ void run(float (&c)[4], unsigned a0, unsigned a2, unsigned b0, unsigned b1) {
+    static __device__ __forceinline__ void run(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
         asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                     : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
     }
 };
 
@@ -111,158 +138,222 @@ __device__ __forceinline__ unsigned atom_add_acq_rel(unsigned* p, unsigned v) {
     return old;
 }
 
-__device__ __forceinline__ void decode_item(const ApplyParams& p, int it, int n_units, bool expand,
-                                            int& unit, int& proj, int& super) {
-    unit = it % n_units;
-    int sp = it / n_units;
-    int pi = 0;
+// Cursor over a CTA's contiguous range of items.  item -> (unit, projection, super-chunk) with
+// unit fastest, so consecutive items are consecutive sub-ranges of one work segment.
+struct Cursor {
+    int unit, sp, proj, super;
+};
+__device__ __forceinline__ void cursor_split(const ApplyParams& p, bool expand, Cursor& c) {
+    int sp = c.sp, pi = 0;
 #pragma unroll
     for (int i = 0; i < kMaxProj; ++i) {
         const int ns = expand ? p.proj[i].n_super_out : p.proj[i].n_super_in;
         if (i < p.n_proj - 1 && pi == i && sp >= ns) { sp -= ns; pi = i + 1; }
     }
-    proj = pi;
-    super = sp;
+    c.proj = pi;
+    c.super = sp;
+}
+__device__ __forceinline__ Cursor cursor_at(const ApplyParams& p, int it, int n_units, bool expand) {
+    Cursor c;
+    c.unit = it % n_units;
+    c.sp = it / n_units;
+    cursor_split(p, expand, c);
+    return c;
+}
+__device__ __forceinline__ void cursor_next(const ApplyParams& p, int n_units, bool expand, Cursor& c) {
+    if (++c.unit == n_units) { c.unit = 0; ++c.sp; cursor_split(p, expand, c); }
 }
 
-// Producer: fetch the unit record of item `it` (lanes 0..15 one word each), derive the meta
-// slot, publish it to shared memory.  Returns with every lane holding the meta in `m`.
-__device__ __forceinline__ void producer_meta(const ApplyParams& p, const PlanView& pv, int it, int n_units,
-                                              bool expand, int lane, Meta* slot) {
-    int unit, proj, super;
-    decode_item(p, it, n_units, expand, unit, proj, super);
-    if (lane < 16) reinterpret_cast<int*>(&slot->u)[lane] = __ldg(pv.unit_tab + (size_t)unit * 16 + lane);
+// What the producer derives for one item; every lane computes it from the broadcast record.
+struct Item {
+    int adapter, rank, sub, ntok, start;
+    long long cum;
+    int proj, c0, valid, kc, n_chunks, width_ok;
+};
+__device__ __forceinline__ Item make_item(const ApplyParams& p, int rec, const Cursor& c, bool expand) {
+    Item it;
+    it.adapter = __shfl_sync(0xffffffffu, rec, 0);
+    it.rank = __shfl_sync(0xffffffffu, rec, 1);
+    const int w2 = __shfl_sync(0xffffffffu, rec, 2);
+    it.sub = w2 & 0xffff;
+    it.ntok = (w2 >> 16) & 0xffff;
+    it.start = __shfl_sync(0xffffffffu, rec, 5);
+    const unsigned lo = (unsigned)__shfl_sync(0xffffffffu, rec, 6);
+    const int hi = __shfl_sync(0xffffffffu, rec, 7);
+    it.cum = ((long long)hi << 32) | lo;
+    const int wshift = it.rank <= 16 ? 9 : it.rank == 32 ? 8 : 7;        // sub-range width 512 / 256 / 128
+    const int h = expand ? p.proj[c.proj].h_out : p.proj[c.proj].h_in;
+    it.proj = c.proj;
+    it.c0 = c.super * kSuper + (it.sub << wshift);
+    it.valid = it.c0 < h;
+    it.kc = it.c0 >> wshift;
+    it.n_chunks = (p.proj[c.proj].h_in + (1 << wshift) - 1) >> wshift;
+    it.width_ok = min(1 << wshift, h - it.c0);
+    return it;
+}
+// lanes 0..15 store the record words, lanes 16..21 the derived fields
+__device__ __forceinline__ void publish_meta(Meta* slot, int rec, const Item& it, int lane) {
+    int* w = reinterpret_cast<int*>(slot);
+    if (lane < 16) w[lane] = rec;
+    else if (lane == 16) w[16] = it.proj;
+    else if (lane == 17) w[17] = it.c0;
+    else if (lane == 18) w[18] = it.valid;
+    else if (lane == 19) w[19] = it.kc;
+    else if (lane == 20) w[20] = it.n_chunks;
+    else if (lane == 21) w[21] = it.width_ok;
     __syncwarp();
-    if (lane == 0) {
-        const int r_pad = pad_rank(slot->u.rank);
-        const int width = kSuper / n_sub(r_pad);
-        const int c0 = super * kSuper + slot->u.sub * width;
-        const int h = expand ? p.proj[proj].h_out : p.proj[proj].h_in;
-        slot->proj = proj;
-        slot->c0 = c0;
-        slot->valid = c0 < h;
-        slot->kc = c0 / width;
-        slot->n_chunks = (p.proj[proj].h_in + width - 1) / width;
-        slot->width_ok = min(width, h - c0);
-    }
-    __syncwarp();
+}
+__device__ __forceinline__ long long item_row0(const ApplyParams& p, const Item& it) {
+    if (p.packed) return (long long)p.n_layers * it.cum + (long long)p.layer * it.rank;
+    return ((long long)it.adapter * p.n_layers + p.layer) * p.r_pool;
 }
 
 // =============================================================================================
 // shrink
 // =============================================================================================
+// Stage layout: weight boxes b = (row group) * ncb + (column block), each [8 rows x 128 cols]
+// contiguous (row pitch 256 B); then the x tile, one row per token, pitch KC*2 + 64 bytes.
 template <typename T>
-__device__ __forceinline__ void shrink_produce(const ApplyParams& p, const Meta& m, unsigned stage, unsigned bar,
-                                               int lane) {
+__device__ __forceinline__ void shrink_produce(const ApplyParams& p, const Item& m, int rec, unsigned stage,
+                                               unsigned bar, int lane) {
     const ProjArgs& pj = p.proj[m.proj];
-    const int r = m.u.rank;
-    const int kc_cols = kSuper / n_sub(r);
-    const unsigned pitch = kc_cols * 2 + kRowPad;
+    const int r = m.rank;
+    const int kc_cols = kSuper / n_sub(r);                // 512, 512, 256, 128
+    const int ncb = kc_cols / kBoxCols;                   // 4, 4, 2, 1
+    const int nbox = ncb * (r / kBoxRows);                // 4, 8, 8, 8
     const unsigned row_bytes = m.width_ok * 2;
-    if (lane == 0) mbar_arrive_expect_tx(bar, row_bytes * (r + m.u.ntok));
+    if (lane == 0) mbar_arrive_expect_tx(bar, nbox * kBoxBytes + m.ntok * row_bytes);
     __syncwarp();
-    const T* A = reinterpret_cast<const T*>(pj.wa) + block_row0(p, m.u) * (long long)pj.h_in + m.c0;
-    for (int row = lane; row < r; row += 32)
-        bulk_g2s(stage + row * pitch, A + (long long)row * pj.h_in, row_bytes, bar);
-    const unsigned xbase = stage + r * pitch;
-    if (lane < m.u.ntok)
-        bulk_g2s(xbase + lane * pitch, reinterpret_cast<const T*>(pj.x) + (long long)m.u.tok[lane] * pj.ldx + m.c0,
-                 row_bytes, bar);
+    if (lane < nbox) {
+        const int rg = lane / ncb, cb = lane - rg * ncb;
+        tensor_g2s_2d(stage + lane * kBoxBytes, &p.amap[m.proj], m.c0 + cb * kBoxCols,
+                      (int)item_row0(p, m) + rg * kBoxRows, bar);
+    }
+    // lanes 8..15 hold the token rows of the unit record
+    if (lane >= 8 && lane < 8 + m.ntok)
+        bulk_g2s(stage + kWTile + (lane - 8) * (kc_cols * 2 + kXPad),
+                 reinterpret_cast<const T*>(pj.x) + (long long)rec * pj.ldx + m.c0, row_bytes, bar);
 }
 
+// Weight rows are the M rows of the MMA (16 per block), the unit's tokens its N columns.  The 8
+// warps = (1, 2 or 4 row blocks) x (8, 4 or 2 slices of the unit's columns); a warp adds 4 MMAs
+// per unit into four independent accumulators that live across the units of one run.
 template <typename T>
-__device__ __forceinline__ void shrink_consume(const ApplyParams& p, const WorkspaceView& ws, const Meta& m,
-                                               const unsigned char* stage, float* red, int tid) {
+__device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid) {
     const int lane = tid & 31, warp = tid >> 5;
     const int r = m.u.rank;
-    const int NB = r / 8;
-    const int nsplit = NB >= 2 ? 2 : 1;
-    const int ksplit = kConsWarps / nsplit;
-    const int NBW = NB / nsplit;                           // 1, 1, 2, 4
+    const int MB = r >= 16 ? r / 16 : 1;                   // 16-row blocks: 1, 1, 2, 4
+    const int ksplit = kConsWarps / MB;                    // 8, 8, 4, 2
     const int kc_cols = kSuper / n_sub(r);
-    const int pitch = kc_cols * 2 + kRowPad;
-    const int kslot = warp % ksplit, nhalf = warp / ksplit;
-    const int nk32 = kc_cols / 32 / ksplit;                // 2, 4, 2, 1
+    const int ncb = kc_cols / kBoxCols;
+    const int kslot = warp % ksplit, mblk = warp / ksplit;
     const int g = lane >> 2, t = lane & 3;
-    const unsigned char* xrow = stage + (r + g) * pitch + t * 16;
-    const unsigned char* wrow = stage + (nhalf * NBW * 8 + g) * pitch + t * 16;
-    const int rp = r + 4;
-    float acc[4][4];
+    const unsigned char* xrow = stage + kWTile + g * (kc_cols * 2 + kXPad) + t * 16;
+    const bool two = r >= 16;                              // rank 8 has no rows 8..15
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    for (int kb = 0; kb < nk32; ++kb) {
-        const int col = (kslot * nk32 + kb) * 32;
+    for (int kb = 0; kb < 2; ++kb) {                        // every warp owns two 32-column blocks
+        const int col = (kslot * 2 + kb) * 32;
         if (col < m.width_ok) {
-            const uint4 xa = *reinterpret_cast<const uint4*>(xrow + col * 2);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (i < NBW) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(wrow + i * 8 * pitch + col * 2);
-                    Mma<T>::run(acc[i], xa.x, xa.y, w.x, w.y);
-                    Mma<T>::run(acc[i], xa.z, xa.w, w.z, w.w);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (i < NBW) {
-            float2* dst = reinterpret_cast<float2*>(red + (kslot * 8 + g) * rp + (nhalf * NBW + i) * 8 + 2 * t);
-            *dst = make_float2(acc[i][0], acc[i][1]);
+            const int cb = col >> 7, cin = col & 127;
+            const unsigned char* wbox = stage + ((mblk * 2) * ncb + cb) * kBoxBytes + g * 256 + cin * 2 + t * 16;
+            const uint4 xb = *reinterpret_cast<const uint4*>(xrow + col * 2);
+            const uint4 w = *reinterpret_cast<const uint4*>(wbox);
+            uint4 u = make_uint4(0u, 0u, 0u, 0u);
+            if (two) u = *reinterpret_cast<const uint4*>(wbox + ncb * kBoxBytes);
+            Mma<T>::run(acc[2 * kb], w.x, u.x, w.y, u.y, xb.x, xb.y);
+            Mma<T>::run(acc[2 * kb + 1], w.z, u.z, w.w, u.w, xb.z, xb.w);
         }
     }
 }
 
+// One run = consecutive units of one (projection, work segment) in this CTA.
+struct Run {
+    int proj, wseg, start, ntok, rank, first_kc, count, n_chunks;
+};
+
+// Ends a run: cross-warp reduction, one split-K partial, arrival; folds if this arrival
+// completed the (projection, work segment).
 template <typename T>
-__device__ __forceinline__ void shrink_publish(const ApplyParams& p, const WorkspaceView& ws, const Meta& m,
-                                               const float* red, int tid) {
-    const int r = m.u.rank, rp = r + 4;
-    const int ksplit = kConsWarps / (r >= 16 ? 2 : 1);
-    const int outs = m.u.ntok * r;
+__device__ __forceinline__ void shrink_flush(const ApplyParams& p, const WorkspaceView& ws, const Run& run,
+                                             float (&acc)[4][4], float* red, int* s_flag, int tid) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int r = run.rank, rp = r + 4;
+    const int MB = r >= 16 ? r / 16 : 1;
+    const int ksplit = kConsWarps / MB;
+    const int kslot = warp % ksplit, mblk = warp / ksplit;
+    const int g = lane >> 2, t = lane & 3;
+    float c[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        c[j] = (acc[0][j] + acc[1][j]) + (acc[2][j] + acc[3][j]);
+        acc[0][j] = acc[1][j] = acc[2][j] = acc[3][j] = 0.f;
+    }
+    // red[kslot][token][rank]: ranks (mblk*16 + g, +8), tokens (2t, 2t+1)
+    float* base = red + kslot * 8 * rp + mblk * 16 + g;
+    base[(2 * t) * rp] = c[0];
+    base[(2 * t + 1) * rp] = c[1];
+    if (r >= 16) {
+        base[(2 * t) * rp + 8] = c[2];
+        base[(2 * t + 1) * rp + 8] = c[3];
+    }
+    cons_sync();
+    const int outs = run.ntok * r;
     const int rshift = 31 - __clz(r);
+    const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
+    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
+    const bool whole = run.count == run.n_chunks;          // this CTA saw every unit of the segment
     for (int idx = tid; idx < outs; idx += kConsThreads) {
         const int tok = idx >> rshift, i = idx & (r - 1);
         float s = 0.f;
         for (int w = 0; w < ksplit; ++w) s += red[(w * 8 + tok) * rp + i];
-        ws.partial[(((size_t)m.kc * p.n_proj + m.proj) * p.cap + (m.u.start + tok)) * kMaxRank + i] = s;
+        const size_t o = ((size_t)run.proj * p.cap + run.start + tok) * kMaxRank + i;
+        if (whole) ws.v[o] = mid_round ? Cvt<T>::round1(s) : s;
+        else ws.partial[(size_t)run.first_kc * cstride + o] = s;
     }
-}
-
-template <typename T>
-__device__ __forceinline__ void shrink_fold(const ApplyParams& p, const WorkspaceView& ws, const Meta& m, int tid) {
-    const int r = m.u.rank;
-    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
-    const int outs = m.u.ntok * r;
-    const int rshift = 31 - __clz(r);
-    const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
-    for (int idx = tid; idx < outs; idx += kConsThreads) {
-        const int pos = m.u.start + (idx >> rshift), i = idx & (r - 1);
-        const float* src = &ws.partial[((size_t)m.proj * p.cap + pos) * kMaxRank + i];
-        float s = 0.f;
-        int c = 0;
-        for (; c + 8 <= m.n_chunks; c += 8) {
-            float v[8];
+    cons_sync();                                           // partial written by all threads, red free again
+    if (whole) return;                                     // nothing to combine across CTAs
+    const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
+    if (tid == 0) {
+        atomicOr(&ws.masks[cidx], 1ull << run.first_kc);
+        const unsigned old = atom_add_acq_rel(&ws.counters[cidx], (unsigned)run.count);
+        *s_flag = (old + (unsigned)run.count == (unsigned)run.n_chunks) ? 1 : 0;
+    }
+    cons_sync();
+    if (*s_flag) {
+        // fold the marked slots in ascending k order
+        const unsigned long long mask = *reinterpret_cast<volatile unsigned long long*>(&ws.masks[cidx]);
+        for (int idx = tid; idx < outs; idx += kConsThreads) {
+            const int pos = run.start + (idx >> rshift), i = idx & (r - 1);
+            const float* src = &ws.partial[((size_t)run.proj * p.cap + pos) * kMaxRank + i];
+            float s = 0.f;
+            unsigned long long mm = mask;
+            while (mm) {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + (size_t)(c + j) * cstride);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += v[j];
+                for (int j = 0; j < 4; ++j) {              // up to four loads in flight, summed in order
+                    if (mm) {
+                        const int kc = __ffsll((long long)mm) - 1;
+                        mm &= mm - 1;
+                        v[j] = __ldcg(src + (size_t)kc * cstride);
+                    }
+                }
+                s = (((s + v[0]) + v[1]) + v[2]) + v[3];
+            }
+            if (mid_round) s = Cvt<T>::round1(s);
+            ws.v[((size_t)run.proj * p.cap + pos) * kMaxRank + i] = s;
         }
-        for (; c < m.n_chunks; ++c) s += __ldcg(src + (size_t)c * cstride);
-        if (mid_round) s = Cvt<T>::round1(s);
-        ws.v[((size_t)m.proj * p.cap + pos) * kMaxRank + i] = s;
+        if (tid == 0) { ws.counters[cidx] = 0u; ws.masks[cidx] = 0ull; }
     }
-    if (tid == 0) ws.counters[(size_t)m.proj * p.cap + m.u.wseg] = 0u;
+    cons_sync();                                           // s_flag may be rewritten by the next flush
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) bgmv_shrink_tma_kernel(const __grid_constant__ ApplyParams p) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(const __grid_constant__ ApplyParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     float* red = reinterpret_cast<float*>(smem + kStages * kShrinkStage);
     Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kShrinkStage + kRedBytes);
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + 2 * kStages);
-    int* s_fold = reinterpret_cast<int*>(bars + 2 * kStages);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
+    int* s_flag = reinterpret_cast<int*>(bars + 2 * kStages);
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -271,98 +362,121 @@ __global__ void __launch_bounds__(kThreads, 1) bgmv_shrink_tma_kernel(const __gr
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_in;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int first = blockIdx.x, stride = gridDim.x;
+    // each CTA takes a contiguous range of items
+    const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int first = blockIdx.x * per_cta;
     if (first >= n_items) return;
-    const int n_local = (n_items - first + stride - 1) / stride;
+    const int n_local = min(per_cta, n_items - first);
     unsigned* err = &ws.ctl->error;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);                 // full: producer's arrive + tx bytes
-            mbar_init(smem_u32(&bars[kStages + s]), 1);       // empty: one consumer thread
+            mbar_init(smem_u32(&bars[kStages + s]), kConsWarps);   // empty: one arrival per consumer warp
         }
-        *s_fold = -1;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == kConsWarps) {
-        // ---------------- producer warp ----------------
-        for (int n = 0; n < n_local; ++n) {
+    if (warp >= kConsWarps) {
+        // ---------------- producer warps ----------------
+        const int pw = warp - kConsWarps;
+        if (pw >= n_local) return;
+        Cursor cur = cursor_at(p, first + pw, n_units, false);
+        int rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
+        TRACE_DECL
+        for (int n = pw; n < n_local; n += kProdWarps) {
+            Cursor nxt = cur;
+#pragma unroll
+            for (int q = 0; q < kProdWarps; ++q) cursor_next(p, n_units, false, nxt);
+            int rec_nxt = 0;                                   // next record: in flight during this item
+            if (n + kProdWarps < n_local && lane < 16) rec_nxt = __ldg(pv.unit_tab + (size_t)nxt.unit * 16 + lane);
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
+            const Item it = make_item(p, rec, cur, false);
+            TRACE_MARK(0)
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 1);
-            Meta* slot = &meta[n % (2 * kStages)];
-            producer_meta(p, pv, first + n * stride, n_units, false, lane, slot);
+            TRACE_MARK(1)
+            publish_meta(&meta[n % kMetaSlots], rec, it, lane);
             const unsigned full = smem_u32(&bars[s]);
-            if (slot->valid) shrink_produce<T>(p, *slot, smem_u32(smem + s * kShrinkStage), full, lane);
+            if (it.valid) shrink_produce<T>(p, it, rec, smem_u32(smem + s * kShrinkStage), full, lane);
             else if (lane == 0) mbar_arrive(full);
+            cur = nxt;
+            rec = rec_nxt;
+            TRACE_MARK(2)
         }
+        TRACE_FLUSH(lane == 0, 0)
         return;
     }
 
     // ---------------- consumer warps ----------------
-    unsigned ticket = 0;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    Run run;
+    run.proj = -1; run.wseg = -1; run.count = 0;
+    run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
+    TRACE_DECL
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
-        const int fold_slot = *s_fold;
-        if (fold_slot >= 0) shrink_fold<T>(p, ws, meta[fold_slot], tid);
-        const Meta& pm = meta[(n + 2 * kStages - 1) % (2 * kStages)];
-        const bool arrive = n > 0 && pm.valid;
-        if (tid == 0 && arrive) ticket = atom_add_acq_rel(&ws.counters[(size_t)pm.proj * p.cap + pm.u.wseg], 1u);
+        TRACE_MARK(0)
         mbar_wait(smem_u32(&bars[s]), ph, err, 2);
-        const Meta& m = meta[n % (2 * kStages)];
-        if (m.valid) shrink_consume<T>(p, ws, m, smem + s * kShrinkStage, red, tid);
-        cons_sync();
-        if (tid == 0) mbar_arrive(smem_u32(&bars[kStages + s]));       // stage is free again
-        if (m.valid) shrink_publish<T>(p, ws, m, red, tid);
-        if (tid == 0) {
-            int f = -1;
-            if (arrive && ticket == (unsigned)(pm.n_chunks - 1)) f = (n + 2 * kStages - 1) % (2 * kStages);
-            *s_fold = f;
+        TRACE_MARK(1)
+        const Meta& m = meta[n % kMetaSlots];
+        if (m.valid) {
+            if (m.proj != run.proj || m.u.wseg != run.wseg) {
+                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid);
+                TRACE_MARK(3)
+                run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
+                run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
+            }
+            shrink_consume<T>(m, smem + s * kShrinkStage, acc, tid);
+            ++run.count;
         }
-        cons_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));      // this warp is done with the stage
+        TRACE_MARK(2)
     }
-    const int last_fold = *s_fold;
-    if (last_fold >= 0) shrink_fold<T>(p, ws, meta[last_fold], tid);
-    cons_sync();
-    const Meta& lm = meta[(n_local - 1) % (2 * kStages)];
-    if (lm.valid) {
-        if (tid == 0) {
-            ticket = atom_add_acq_rel(&ws.counters[(size_t)lm.proj * p.cap + lm.u.wseg], 1u);
-            *s_fold = (ticket == (unsigned)(lm.n_chunks - 1)) ? 1 : 0;
-        }
-        cons_sync();
-        if (*s_fold == 1) shrink_fold<T>(p, ws, lm, tid);
-    }
+    if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid);
+    TRACE_MARK(3)
+    TRACE_FLUSH(tid == 0, 5)
 }
 
 // =============================================================================================
 // expand
 // =============================================================================================
 template <typename T>
-__device__ __forceinline__ void expand_produce(const ApplyParams& p, const WorkspaceView& ws, const Meta& m,
+__device__ __forceinline__ void expand_produce(const ApplyParams& p, const WorkspaceView& ws, const Item& m, int rec,
                                                unsigned stage, unsigned bar, int lane) {
     const ProjArgs& pj = p.proj[m.proj];
-    const int r = m.u.rank;
+    const int r = m.rank;
     const int jc = kSuper / n_sub(r);
     const unsigned w_bytes = m.width_ok * r * 2;
     const unsigned y_bytes = p.y_f32 ? 0u : m.width_ok * 2;
     const unsigned v_bytes = r * 4;
-    if (lane == 0) mbar_arrive_expect_tx(bar, w_bytes + m.u.ntok * (y_bytes + v_bytes));
+    if (lane == 0) mbar_arrive_expect_tx(bar, w_bytes + m.ntok * (y_bytes + v_bytes));
     __syncwarp();
+    // one instruction: lane 0 the weight tile, lanes 8..15 the y rows, lanes 16..23 the v rows
+    const int tok = __shfl_sync(0xffffffffu, rec, 8 + (lane & 7));
+    unsigned dst = 0, bytes = 0;
+    const void* src = pj.wb;
     if (lane == 0) {
-        const T* B = reinterpret_cast<const T*>(pj.wb) + (block_row0(p, m.u) * (long long)pj.h_out + (long long)m.c0 * r);
-        bulk_g2s(stage, B, w_bytes, bar);
+        dst = stage;
+        src = reinterpret_cast<const T*>(pj.wb) + (item_row0(p, m) * (long long)pj.h_out + (long long)m.c0 * r);
+        bytes = w_bytes;
+    } else if (lane >= 8 && lane < 8 + m.ntok) {
+        dst = stage + kWTile + (lane - 8) * (jc * 2 + kYPad);
+        src = reinterpret_cast<const T*>(pj.y) + (long long)tok * pj.ldy + m.c0;
+        bytes = y_bytes;
+    } else if (lane >= 16 && lane < 16 + m.ntok) {
+        dst = stage + kWTile + kYBytes + (lane - 16) * (kVPitch * 4);
+        src = ws.v + ((size_t)m.proj * p.cap + m.start + (lane - 16)) * kMaxRank;
+        bytes = v_bytes;
     }
-    if (lane < m.u.ntok) {
-        if (y_bytes)
-            bulk_g2s(stage + 32768 + lane * (jc * 2 + kYPad),
-                     reinterpret_cast<const T*>(pj.y) + (long long)m.u.tok[lane] * pj.ldy + m.c0, y_bytes, bar);
-        bulk_g2s(stage + 32768 + kYBytes + lane * (kVPitch * 4),
-                 ws.v + ((size_t)m.proj * p.cap + m.u.start + lane) * kMaxRank, v_bytes, bar);
-    }
+    if (bytes) bulk_g2s(dst, src, bytes, bar);
 }
 
 // hi/lo split of two fp32 values into packed 16-bit pairs
@@ -373,24 +487,29 @@ __device__ __forceinline__ void split2(float v0, float v1, unsigned& hi, unsigne
     lo = Cvt<T>::pack2(v0 - h0, v1 - h1);
 }
 
-// R = rank class.  Thread (g, t) of a warp owns, for token g and output rows (8*block + 2t, +1):
+// R = rank class.  The MMA's M rows 0..7 hold the hi halves of the tokens' intermediate and rows
+// 8..15 the lo halves, so one MMA yields both products.  Thread (g, t) owns, for token g and
+// output rows (8*block + 2t, +1):
 //   R=64: chunks 2t and 2t+1 of each 128-byte weight row (4 MMA k-steps)
 //   R=32: chunk t of each 64-byte row (2 k-steps);  R=16: 8 bytes (1 k-step);  R=8: 4 bytes.
+// All of a warp's MMAs are issued before any result is used.
 template <typename T, int R>
 __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid) {
     constexpr int CALLS = R == 64 ? 4 : R == 32 ? 2 : 1;
-    constexpr int JC = kSuper / (R <= 16 ? 2 : R / 8);
-    constexpr int NBW = JC / 8 / kConsWarps;
+    constexpr int JC = kSuper / (R <= 16 ? 4 : R / 4);
+    constexpr int NBW = JC / 8 / kConsWarps;               // 8-row blocks per warp: 8, 8, 4, 2
     const ProjArgs& pj = p.proj[m.proj];
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int ntok = m.u.ntok;
     const float scale = m.u.scale;
-    const float* vt = reinterpret_cast<const float*>(stage + 32768 + kYBytes) + g * kVPitch;
+    const float* vt = reinterpret_cast<const float*>(stage + kWTile + kYBytes) + g * kVPitch;
 
     unsigned ah[CALLS][2], al[CALLS][2];
+#pragma unroll
+    for (int c = 0; c < CALLS; ++c) { ah[c][0] = ah[c][1] = al[c][0] = al[c][1] = 0u; }
     if (g < ntok) {
-        if (R == 64) {
+        if constexpr (R == 64) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const float4 lo4 = *reinterpret_cast<const float4*>(vt + (2 * t + c) * 8);
@@ -400,58 +519,60 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
                 split2<T>(hi4.x, hi4.y, ah[2 * c + 1][0], al[2 * c + 1][0]);
                 split2<T>(hi4.z, hi4.w, ah[2 * c + 1][1], al[2 * c + 1][1]);
             }
-        } else if (R == 32) {
+        } else if constexpr (R == 32) {
             const float4 lo4 = *reinterpret_cast<const float4*>(vt + t * 8);
             const float4 hi4 = *reinterpret_cast<const float4*>(vt + t * 8 + 4);
             split2<T>(lo4.x, lo4.y, ah[0][0], al[0][0]);
             split2<T>(lo4.z, lo4.w, ah[0][1], al[0][1]);
-            split2<T>(hi4.x, hi4.y, ah[CALLS - 1][0], al[CALLS - 1][0]);
-            split2<T>(hi4.z, hi4.w, ah[CALLS - 1][1], al[CALLS - 1][1]);
-        } else if (R == 16) {
+            split2<T>(hi4.x, hi4.y, ah[1][0], al[1][0]);
+            split2<T>(hi4.z, hi4.w, ah[1][1], al[1][1]);
+        } else if constexpr (R == 16) {
             const float4 v4 = *reinterpret_cast<const float4*>(vt + t * 4);
             split2<T>(v4.x, v4.y, ah[0][0], al[0][0]);
             split2<T>(v4.z, v4.w, ah[0][1], al[0][1]);
         } else {
             const float2 v2 = *reinterpret_cast<const float2*>(vt + t * 2);
             split2<T>(v2.x, v2.y, ah[0][0], al[0][0]);
-            ah[0][1] = 0u; al[0][1] = 0u;
         }
-    } else {
-#pragma unroll
-        for (int c = 0; c < CALLS; ++c) { ah[c][0] = ah[c][1] = al[c][0] = al[c][1] = 0u; }
     }
 
-    unsigned char* ysb = stage + 32768;
-    constexpr int ypitch = JC * 2 + kYPad;
     const int jbase = warp * NBW * 8;
-#pragma unroll 2
+    float acc[NBW][CALLS][4];
+#pragma unroll
     for (int nb = 0; nb < NBW; ++nb) {
-        const int jrow = jbase + nb * 8 + g;                 // this thread's weight row (N index g)
-        const unsigned char* wr = stage + jrow * (R * 2);
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        if (R == 64) {
+#pragma unroll
+        for (int c = 0; c < CALLS; ++c) { acc[nb][c][0] = acc[nb][c][1] = acc[nb][c][2] = acc[nb][c][3] = 0.f; }
+        const unsigned char* wr = stage + (jbase + nb * 8 + g) * (R * 2);    // this thread's weight row (N index g)
+        if constexpr (R == 64) {
             const uint4 w0 = *reinterpret_cast<const uint4*>(wr + (2 * t) * 16);
             const uint4 w1 = *reinterpret_cast<const uint4*>(wr + (2 * t + 1) * 16);
-            Mma<T>::run(acc, ah[0][0], ah[0][1], w0.x, w0.y); Mma<T>::run(acc, al[0][0], al[0][1], w0.x, w0.y);
-            Mma<T>::run(acc, ah[1][0], ah[1][1], w0.z, w0.w); Mma<T>::run(acc, al[1][0], al[1][1], w0.z, w0.w);
-            Mma<T>::run(acc, ah[2][0], ah[2][1], w1.x, w1.y); Mma<T>::run(acc, al[2][0], al[2][1], w1.x, w1.y);
-            Mma<T>::run(acc, ah[3][0], ah[3][1], w1.z, w1.w); Mma<T>::run(acc, al[3][0], al[3][1], w1.z, w1.w);
-        } else if (R == 32) {
+            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], ah[0][1], al[0][1], w0.x, w0.y);
+            Mma<T>::run(acc[nb][1], ah[1][0], al[1][0], ah[1][1], al[1][1], w0.z, w0.w);
+            Mma<T>::run(acc[nb][2], ah[2][0], al[2][0], ah[2][1], al[2][1], w1.x, w1.y);
+            Mma<T>::run(acc[nb][3], ah[3][0], al[3][0], ah[3][1], al[3][1], w1.z, w1.w);
+        } else if constexpr (R == 32) {
             const uint4 w0 = *reinterpret_cast<const uint4*>(wr + t * 16);
-            Mma<T>::run(acc, ah[0][0], ah[0][1], w0.x, w0.y); Mma<T>::run(acc, al[0][0], al[0][1], w0.x, w0.y);
-            Mma<T>::run(acc, ah[CALLS - 1][0], ah[CALLS - 1][1], w0.z, w0.w);
-            Mma<T>::run(acc, al[CALLS - 1][0], al[CALLS - 1][1], w0.z, w0.w);
-        } else if (R == 16) {
+            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], ah[0][1], al[0][1], w0.x, w0.y);
+            Mma<T>::run(acc[nb][1], ah[1][0], al[1][0], ah[1][1], al[1][1], w0.z, w0.w);
+        } else if constexpr (R == 16) {
             const uint2 w0 = *reinterpret_cast<const uint2*>(wr + t * 8);
-            Mma<T>::run(acc, ah[0][0], ah[0][1], w0.x, w0.y); Mma<T>::run(acc, al[0][0], al[0][1], w0.x, w0.y);
+            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], ah[0][1], al[0][1], w0.x, w0.y);
         } else {
             const unsigned w0 = *reinterpret_cast<const unsigned*>(wr + t * 4);
-            Mma<T>::run(acc, ah[0][0], 0u, w0, 0u); Mma<T>::run(acc, al[0][0], 0u, w0, 0u);
+            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], 0u, 0u, w0, 0u);
         }
-        // y[token g][j, j+1] += scale * acc
+    }
+    // y[token g][j, j+1] += scale * (hi + lo products)
+    unsigned char* ysb = stage + kWTile;
+    constexpr int ypitch = JC * 2 + kYPad;
+#pragma unroll
+    for (int nb = 0; nb < NBW; ++nb) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CALLS; ++c) { s0 += acc[nb][c][0] + acc[nb][c][2]; s1 += acc[nb][c][1] + acc[nb][c][3]; }
         const int j = jbase + nb * 8 + 2 * t;
         if (g < ntok && j < m.width_ok) {
-            const float d0 = scale * acc[0], d1 = scale * acc[1];
+            const float d0 = scale * s0, d1 = scale * s1;
             if (p.y_f32) {
                 float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + (long long)m.u.tok[g] * pj.ldy + m.c0 + j);
                 float2 yv = *yp;
@@ -474,10 +595,10 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) bgmv_expand_tma_kernel(const __grid_constant__ ApplyParams p) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(const __grid_constant__ ApplyParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kExpandStage);
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + 2 * kStages);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -486,9 +607,10 @@ __global__ void __launch_bounds__(kThreads, 1) bgmv_expand_tma_kernel(const __gr
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_out;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int first = blockIdx.x, stride = gridDim.x;
+    const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int first = blockIdx.x * per_cta;
     if (first >= n_items) return;
-    const int n_local = (n_items - first + stride - 1) / stride;
+    const int n_local = min(per_cta, n_items - first);
     unsigned* err = &ws.ctl->error;
 
     if (tid == 0) {
@@ -500,25 +622,44 @@ __global__ void __launch_bounds__(kThreads, 1) bgmv_expand_tma_kernel(const __gr
     }
     __syncthreads();
 
-    if (warp == kConsWarps) {
-        for (int n = 0; n < n_local; ++n) {
+    if (warp >= kConsWarps) {
+        const int pw = warp - kConsWarps;
+        if (pw >= n_local) return;
+        Cursor cur = cursor_at(p, first + pw, n_units, true);
+        int rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
+        TRACE_DECL
+        for (int n = pw; n < n_local; n += kProdWarps) {
+            Cursor nxt = cur;
+#pragma unroll
+            for (int q = 0; q < kProdWarps; ++q) cursor_next(p, n_units, true, nxt);
+            int rec_nxt = 0;
+            if (n + kProdWarps < n_local && lane < 16) rec_nxt = __ldg(pv.unit_tab + (size_t)nxt.unit * 16 + lane);
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
+            const Item it = make_item(p, rec, cur, true);
+            TRACE_MARK(0)
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
-            Meta* slot = &meta[n % (2 * kStages)];
-            producer_meta(p, pv, first + n * stride, n_units, true, lane, slot);
+            TRACE_MARK(1)
+            publish_meta(&meta[n % kMetaSlots], rec, it, lane);
             const unsigned full = smem_u32(&bars[s]);
-            if (slot->valid) expand_produce<T>(p, ws, *slot, smem_u32(smem + s * kExpandStage), full, lane);
+            if (it.valid) expand_produce<T>(p, ws, it, rec, smem_u32(smem + s * kExpandStage), full, lane);
             else if (lane == 0) mbar_arrive(full);
+            cur = nxt;
+            rec = rec_nxt;
+            TRACE_MARK(2)
         }
+        TRACE_FLUSH(lane == 0, 0)
         return;
     }
 
+    TRACE_DECL
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
+        TRACE_MARK(0)
         mbar_wait(smem_u32(&bars[s]), ph, err, 4);
-        const Meta& m = meta[n % (2 * kStages)];
+        TRACE_MARK(1)
+        const Meta& m = meta[n % kMetaSlots];
         unsigned char* stage = smem + s * kExpandStage;
         if (m.valid) {
             switch (m.u.rank) {
@@ -528,7 +669,9 @@ __global__ void __launch_bounds__(kThreads, 1) bgmv_expand_tma_kernel(const __gr
                 default: expand_consume<T, 64>(p, m, stage, tid); break;
             }
         }
+        TRACE_MARK(2)
         cons_sync();
+        TRACE_MARK(3)
         if (m.valid && !p.y_f32) {
             // coalesced write-back of the updated y tile, 16 bytes per thread
             const ProjArgs& pj = p.proj[m.proj];
@@ -537,19 +680,22 @@ __global__ void __launch_bounds__(kThreads, 1) bgmv_expand_tma_kernel(const __gr
             const int c = tid & (cpt - 1), rstep = kConsThreads >> cpt_shift;
             if (c * 8 < m.width_ok) {
                 for (int row = tid >> cpt_shift; row < m.u.ntok; row += rstep) {
-                    const uint4 val = *reinterpret_cast<const uint4*>(stage + 32768 + row * (jc * 2 + kYPad) + c * 16);
+                    const uint4 val = *reinterpret_cast<const uint4*>(stage + kWTile + row * (jc * 2 + kYPad) + c * 16);
                     *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + c * 8) = val;
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));     // one arrival per consumer warp
+        TRACE_MARK(4)
     }
+    TRACE_FLUSH(tid == 0, 5)
 }
 
-constexpr int kShrinkSmem = kStages * kShrinkStage + kRedBytes + 2 * kStages * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
-constexpr int kExpandSmem = kStages * kExpandStage + 2 * kStages * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
-static_assert(kShrinkSmem <= 232448 && kExpandSmem <= 232448, "exceeds the 227 KB shared memory of one CTA");
+constexpr int kShrinkSmem = kStages * kShrinkStage + kRedBytes + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
+constexpr int kExpandSmem = kStages * kExpandStage + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
+static_assert(kCtasPerSm * (kShrinkSmem + 1024) <= 233472 && kCtasPerSm * (kExpandSmem + 1024) <= 233472,
+              "two CTAs must fit the 228 KB of shared memory of one SM");
 
 template <typename T>
 cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
@@ -563,8 +709,9 @@ cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    if (!(p.flags & B200_LORA_ONLY_EXPAND)) bgmv_shrink_tma_kernel<T><<<n_sm, kThreads, kShrinkSmem, s>>>(p);
-    if (!(p.flags & B200_LORA_ONLY_SHRINK)) bgmv_expand_tma_kernel<T><<<n_sm, kThreads, kExpandSmem, s>>>(p);
+    const int grid = n_sm * kCtasPerSm;
+    if (!(p.flags & B200_LORA_ONLY_EXPAND)) bgmv_shrink_tma_kernel<T><<<grid, kThreads, kShrinkSmem, s>>>(p);
+    if (!(p.flags & B200_LORA_ONLY_SHRINK)) bgmv_expand_tma_kernel<T><<<grid, kThreads, kExpandSmem, s>>>(p);
     return cudaGetLastError();
 }
 

@@ -1,6 +1,7 @@
 // Shared device/host definitions of the multi-LoRA delta kernels (sm_100a).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -12,6 +13,7 @@ namespace b200lora {
 
 constexpr int kMaxRank = B200_LORA_MAX_RANK;   // 64
 constexpr int kMaxProj = B200_LORA_MAX_PROJ;   // 4
+constexpr int kMaxSub = 16;                    // most sub-ranges of one super-chunk (rank 64)
 constexpr int kSuper = 2048;                   // columns (shrink) / rows (expand) per super-chunk
 constexpr int kCtaThreads = 512;
 constexpr int kChunkTok = 8;                   // BGMV work segments hold at most this many tokens
@@ -60,7 +62,7 @@ struct PlanView {
     int* ws_start;      // [cap + 1]   work segments: adapter segments cut into <= kChunkTok tokens
     int* ws_adapter;    // [cap]
     int* ws_rank;       // [cap]
-    int* unit_tab;      // [8 * cap][16]  one record per 32 KB weight unit (see UnitRec)
+    int* unit_tab;      // [16 * cap][16]  one record per weight unit (see UnitRec)
     int* tile_tab;      // [cap]       (seg << 12) | m-tile, for tall segments (cap/kTallMin used)
     int* hist;          // [n_adapters + 1]
 };
@@ -68,7 +70,7 @@ struct PlanView {
 __host__ __device__ inline size_t plan_words(int cap, int n_adapters) {
     // header + perm + seg_start + 3 seg arrays + units + tiles + hist, each padded to 4 words
     auto pad4 = [](size_t w) { return (w + 3) & ~size_t(3); };
-    return 16 + pad4(cap) + 2 * pad4(cap + 1) + 5 * pad4(cap) + 16 * 8 * (size_t)cap + pad4(cap) +
+    return 16 + pad4(cap) + 2 * pad4(cap + 1) + 5 * pad4(cap) + 16 * kMaxSub * (size_t)cap + pad4(cap) +
            pad4((size_t)n_adapters + 1);
 }
 
@@ -85,7 +87,7 @@ __host__ __device__ inline PlanView plan_view(void* base, int cap, int n_adapter
     v.ws_start = w;                                w += pad4(cap + 1);
     v.ws_adapter = w;                              w += pad4(cap);
     v.ws_rank = w;                                 w += pad4(cap);
-    v.unit_tab = w;                                w += 16 * 8 * (size_t)cap;
+    v.unit_tab = w;                                w += 16 * kMaxSub * (size_t)cap;
     v.tile_tab = w;                                w += pad4(cap);
     v.hist = w;
     (void)n_adapters;
@@ -103,12 +105,12 @@ struct WorkspaceCtl {
 };
 static_assert(sizeof(WorkspaceCtl) == 64, "control block is 16 words");
 
-__host__ __device__ inline int max_kchunks(int h_in) { return (h_in + 255) / 256; }
+__host__ __device__ inline int max_kchunks(int h_in) { return (h_in + 127) / 128; }
 
 __host__ __device__ inline size_t ws_counter_words(int cap) { return (size_t)kMaxProj * cap; }
 
 __host__ __device__ inline size_t workspace_bytes(int cap, int n_proj, int max_h_in) {
-    size_t ctl = sizeof(WorkspaceCtl) + 4 * ((ws_counter_words(cap) + 3) & ~size_t(3));
+    size_t ctl = sizeof(WorkspaceCtl) + 4 * ((ws_counter_words(cap) + 3) & ~size_t(3)) + 8 * ws_counter_words(cap);
     size_t v = (size_t)n_proj * cap * kMaxRank * 4;
     size_t part = (size_t)max_kchunks(max_h_in) * n_proj * cap * kMaxRank * 4;
     return ctl + v + part + 256;
@@ -116,7 +118,8 @@ __host__ __device__ inline size_t workspace_bytes(int cap, int n_proj, int max_h
 
 struct WorkspaceView {
     WorkspaceCtl* ctl;
-    unsigned* counters;   // [kMaxProj][cap]  arrivals per (projection, segment)
+    unsigned* counters;   // [kMaxProj][cap]  arrivals per (projection, work segment)
+    unsigned long long* masks;   // [kMaxProj][cap]  split-K slots published per (projection, work segment)
     float* v;             // [n_proj][cap][64]
     float* partial;       // [kchunk][n_proj][cap][64]
 };
@@ -126,6 +129,7 @@ __host__ __device__ inline WorkspaceView workspace_view(void* base, int cap, int
     WorkspaceView w;
     w.ctl = reinterpret_cast<WorkspaceCtl*>(p);            p += sizeof(WorkspaceCtl);
     w.counters = reinterpret_cast<unsigned*>(p);           p += 4 * ((ws_counter_words(cap) + 3) & ~size_t(3));
+    w.masks = reinterpret_cast<unsigned long long*>(p);    p += 8 * ws_counter_words(cap);
     p = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(p) + 127) & ~uintptr_t(127));
     w.v = reinterpret_cast<float*>(p);                     p += (size_t)n_proj * cap * kMaxRank * 4;
     w.partial = reinterpret_cast<float*>(p);
@@ -144,6 +148,7 @@ struct ProjArgs {
 };
 
 struct ApplyParams {
+    alignas(64) CUtensorMap amap[kMaxProj];   // 2-D maps over the A pools ([rows, h_in], box 128 x 8); TMA kernels only
     ProjArgs proj[kMaxProj];
     int n_proj;
     int total_super_in, total_super_out;
@@ -173,8 +178,10 @@ __device__ __forceinline__ long long block_row0(const ApplyParams& p, const Unit
 __device__ __forceinline__ int b_pitch(const ApplyParams& p, int r) { return p.packed ? r : p.r_pool; }
 
 __host__ __device__ __forceinline__ int pad_rank(int r) { return r <= 8 ? 8 : r <= 16 ? 16 : r <= 32 ? 32 : 64; }
-// sub-ranges per 2048-wide super-chunk for a padded rank: 8->2, 16->2, 32->4, 64->8
-__host__ __device__ __forceinline__ int n_sub(int r_pad) { return r_pad <= 16 ? 2 : r_pad / 8; }
+// sub-ranges per 2048-wide super-chunk for a padded rank: 8->4, 16->4, 32->8, 64->16, i.e. a unit is
+// 512 / 512 / 256 / 128 columns (shrink) or rows (expand) wide and holds <= 16 KB of weights
+__host__ __device__ __forceinline__ int n_sub(int r_pad) { return r_pad <= 16 ? 4 : r_pad / 4; }
+
 
 // ---- 16-bit -> fp32 helpers ------------------------------------------------------------------
 template <typename T> struct Cvt;

@@ -3,7 +3,7 @@
 // One CTA turns the per-token adapter ids into
 //   perm         stable counting sort (token order kept inside one adapter)
 //   seg_*        one segment per adapter that has tokens, ascending adapter id
-//   unit_tab     the 32 KB weight units the BGMV kernels walk: short segments first
+//   unit_tab     the <= 16 KB weight units the BGMV kernels walk: short segments first
 //   tile_tab     128-row tiles of tall contiguous segments for the tensor-core kernel
 // It replaces the reference's precomputed index tensor (lightllm/models/lora_gpu.py:120,124)
 // and is integer work only: the tests require it bit-exact against a stable argsort.

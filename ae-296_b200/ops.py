@@ -34,12 +34,13 @@ def _require_cuda(*tensors):
 
 
 def _adapters_struct(n_adapters, n_layers, r_pool, ranks=None, scalings=None, cum_ranks=None,
-                     packed=False, scale=1.0, ranks_pow2=False) -> Adapters:
+                     packed=False, scale=1.0, ranks_pow2=False, total_rank=0) -> Adapters:
     return Adapters(
         ranks.data_ptr() if ranks is not None else None,
         scalings.data_ptr() if scalings is not None else None,
         cum_ranks.data_ptr() if cum_ranks is not None else None,
-        n_adapters, n_layers, r_pool, 1 if packed else 0, float(scale), 1 if ranks_pow2 else 0)
+        n_adapters, n_layers, r_pool, 1 if packed else 0, float(scale), 1 if ranks_pow2 else 0,
+        int(total_rank))
 
 
 def adapters_of(pool: AdapterPool) -> Adapters:
@@ -51,7 +52,7 @@ def adapters_of(pool: AdapterPool) -> Adapters:
     else:
         pow2 = bool((rh == pool.r_pool).all()) and pool.r_pool in (8, 16, 32, 64)
     return _adapters_struct(pool.n_adapters, pool.n_layers, pool.r_pool, pool.ranks, pool.scalings,
-                            pool.cum_ranks, pool.packed, 1.0, pow2)
+                            pool.cum_ranks, pool.packed, 1.0, pow2, int(pool.cum_host[-1]))
 
 
 class LoraPlan:

@@ -70,6 +70,7 @@ typedef struct b200_lora_adapters {
                                   when dense); selects the TMA kernels.  Checked on the device when a
                                   plan is built: a broken promise yields B200_LORA_ERR_RANK from
                                   b200_lora_plan_read and a plan that applies nothing. */
+    int64_t total_rank;        /* sum of all ranks (packed pools); 0 = not known */
 } b200_lora_adapters;
 
 /* One projection (q, k, v or o): replaces one (x, pool pair, y) triple of

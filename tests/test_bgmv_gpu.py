@@ -95,10 +95,18 @@ def test_fused_qkv_equals_separate_calls():
     batch = L.LoraBatch(48, 12, 1024, 3).set_ids(c.ids_dev, c.pool)
     batch.apply([(c.x, ys[0], c.pool), (c.x, ys[1], k.pool), (c.x, ys[2], c.pool)], 1)
     torch.cuda.synchronize()
-    assert torch.equal(ys[0], c.run(1))
-    assert torch.equal(ys[2], ys[0])
+    batch.workspace.check()
+
+    def close(a, b):
+        # the fused call cuts the split-K sums at other places than a single-projection call,
+        # so the fp32 sums may differ in their last bits: allow one fp16 ulp of the result
+        a, b = a.float(), b.float()
+        return bool(((a - b).abs() <= 2.0 ** -10 * b.abs().clamp_min(2.0 ** -6)).all())
+
+    assert close(ys[0], c.run(1))
+    assert close(ys[2], ys[0])
     k.x, k.x_cpu = c.x, c.x_cpu
-    assert torch.equal(ys[1], k.run(1))
+    assert close(ys[1], k.run(1))
 
 
 def test_errors_are_raised_not_swallowed():
