@@ -57,8 +57,8 @@ SYMBOLS = {
     "b200_lora_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "b200_lora_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_lora_apply": (C.c_int, [C.POINTER(Proj), C.c_int32, C.POINTER(Adapters), C.c_void_p, C.c_int32,
-                                  C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t,
-                                  C.c_void_p]),
+                                  C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                  C.c_size_t, C.c_void_p]),
     "b200_add_lora_bgmv_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "b200_add_lora_bgmv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                      C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,

@@ -47,24 +47,26 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// 2-D map over a row-major 16-bit matrix [rows, inner]; cached per (base, inner, rows, box)
+// 2-D map over a row-major 16-bit matrix [rows, inner] with row pitch `pitch` elements;
+// cached per (base, shape, box)
 bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner,
-                   uint32_t box_rows, CUtensorMapSwizzle swizzle) {
-    struct Entry { const void* base; uint64_t inner, rows; uint32_t bi, br; int sw; CUtensorMap map; };
+                   uint32_t box_rows, CUtensorMapSwizzle swizzle, uint64_t pitch = 0) {
+    if (pitch == 0) pitch = inner;
+    struct Entry { const void* base; uint64_t inner, rows, pitch; uint32_t bi, br; int sw; CUtensorMap map; };
     static Entry cache[64];
     static int n_cached = 0, next = 0;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
     for (int i = 0; i < n_cached; ++i) {
         const Entry& e = cache[i];
-        if (e.base == base && e.inner == inner && e.rows == rows && e.bi == box_inner && e.br == box_rows &&
+        if (e.base == base && e.inner == inner && e.rows == rows && e.pitch == pitch && e.bi == box_inner && e.br == box_rows &&
             e.sw == (int)swizzle) { *out = e.map; return true; }
     }
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
     alignas(64) CUtensorMap m;
     cuuint64_t dims[2] = {inner, rows};
-    cuuint64_t strides[1] = {inner * 2};
+    cuuint64_t strides[1] = {pitch * 2};
     cuuint32_t box[2] = {box_inner, box_rows};
     cuuint32_t estr[2] = {1, 1};
     if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -72,7 +74,7 @@ bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t 
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
     Entry& e = cache[next];
-    e.base = base; e.inner = inner; e.rows = rows; e.bi = box_inner; e.br = box_rows; e.sw = (int)swizzle; e.map = m;
+    e.base = base; e.inner = inner; e.rows = rows; e.pitch = pitch; e.bi = box_inner; e.br = box_rows; e.sw = (int)swizzle; e.map = m;
     next = (next + 1) % 64;
     if (n_cached < 64) ++n_cached;
     *out = m;
@@ -199,12 +201,12 @@ int b200_lora_workspace_init(void* workspace, size_t bytes, void* stream) {
 }
 
 int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
-                    const void* plan, int32_t max_tokens, int32_t layer, int32_t io_dtype, int32_t y_dtype,
-                    int32_t flags, void* workspace, size_t workspace_bytes_, void* stream) {
+                    const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
+                    int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes_, void* stream) {
     if (!projs || !plan || !workspace) return B200_LORA_ERR_NULL;
     int rc = check_adapters(adapters);
     if (rc) return rc;
-    if (n_proj < 1 || n_proj > kMaxProj || max_tokens < 1) return B200_LORA_ERR_DIM;
+    if (n_proj < 1 || n_proj > kMaxProj || max_tokens < 1 || n_tokens < 1 || n_tokens > max_tokens) return B200_LORA_ERR_DIM;
     if (io_dtype != B200_LORA_F16 && io_dtype != B200_LORA_BF16) return B200_LORA_ERR_DTYPE;
     if (y_dtype != io_dtype && y_dtype != B200_LORA_F32) return B200_LORA_ERR_DTYPE;
     if (layer < 0 || layer >= adapters->n_layers) return B200_LORA_ERR_LAYER;
@@ -249,7 +251,28 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     const int n_sm = sm_count();
     cudaError_t e = cudaSuccess;
     if (!sgmv_tiles_supported(p)) p.flags |= B200_LORA_NO_TENSOR;
-    if (!(p.flags & B200_LORA_NO_TENSOR)) e = launch_sgmv_tiles(p, io_dtype, n_sm, s);
+    if (!(p.flags & B200_LORA_NO_TENSOR)) {
+        SgmvParams sp;
+        memset(&sp, 0, sizeof(sp));
+        bool ok = true;
+        const uint64_t arows = pool_rows(adapters);
+        for (int i = 0; i < n_proj && ok; ++i) {
+            const b200_lora_proj& q = projs[i];
+            ok = tensor_map_2d(&sp.xmap[i], q.x, (uint64_t)q.h_in, (uint64_t)n_tokens, 64, 128,
+                               CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)q.ldx) &&
+                 tensor_map_2d(&sp.amap[i], q.wa, (uint64_t)q.h_in, arows, 64, 8, CU_TENSOR_MAP_SWIZZLE_128B);
+            for (int c = 0; c < 3 && ok; ++c) {
+                const uint64_t rc = 16u << c;
+                if (!adapters->packed && rc != (uint64_t)adapters->r_pool) continue;   // dense pools have one rank
+                const uint64_t brows = arows * (uint64_t)q.h_out / rc;
+                const CUtensorMapSwizzle sw = c == 0 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                            : c == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+                ok = tensor_map_2d(&sp.bmap[i][c], q.wb, rc, brows, (uint32_t)rc, 128, sw);
+            }
+        }
+        if (!ok) p.flags |= B200_LORA_NO_TENSOR;        // no driver entry point: everything on the BGMV kernels
+        else e = launch_sgmv_tiles(p, sp, io_dtype, n_sm, s);
+    }
     bool fast = fast_ranks(adapters);
     for (int i = 0; i < n_proj; ++i)
         if ((projs[i].h_in % 256) || (projs[i].h_out % 256) || projs[i].h_in > 8192) fast = false;
@@ -297,7 +320,7 @@ int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void*
     b200_lora_proj pj;
     pj.x = x; pj.y = y; pj.wa = wa_T_all; pj.wb = wb_T_all;
     pj.ldx = h_in; pj.ldy = h_out; pj.h_in = h_in; pj.h_out = h_out;
-    return b200_lora_apply(&pj, 1, &ad, workspace, n_tokens, layer_idx, dtype, dtype, 0, ws,
+    return b200_lora_apply(&pj, 1, &ad, workspace, n_tokens, n_tokens, layer_idx, dtype, dtype, B200_LORA_NO_TENSOR, ws,
                            workspace_bytes_ - pb, stream);
 }
 

@@ -165,6 +165,13 @@ struct ApplyParams {
     void* workspace;
 };
 
+// Tensor maps of the tcgen05 tile kernel (all over local memory).
+struct SgmvParams {
+    alignas(64) CUtensorMap xmap[kMaxProj];      // x [T, h_in], box 64 x 128, 128-byte swizzle
+    CUtensorMap amap[kMaxProj];                  // A pool [rows, h_in], box 64 x 8, 128-byte swizzle
+    CUtensorMap bmap[kMaxProj][3];               // B pool viewed as [rows, 16 | 32 | 64], box rank x 128
+};
+
 // element offset of adapter a's A block [r, h] for `layer`, and its row count / row pitch
 __device__ __forceinline__ long long block_row0(const ApplyParams& p, int a, int r) {
     if (p.packed) return (long long)p.n_layers * p.cum_ranks[a] + (long long)p.layer * r;
@@ -237,6 +244,6 @@ cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts
 cudaError_t launch_bgmv(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
 cudaError_t launch_bgmv_tma(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
 bool sgmv_tiles_supported(const ApplyParams& p);
-cudaError_t launch_sgmv_tiles(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
+cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io_dtype, int n_sm, cudaStream_t s);
 
 }  // namespace b200lora

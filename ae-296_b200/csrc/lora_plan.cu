@@ -137,7 +137,9 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
                 int e = pv.seg_start[s + 1];
                 len = e - b;
                 bool contig = identity || (pv.perm[e - 1] - pv.perm[b] == len - 1);
-                tall = (len >= kTallMin && contig) ? 1 : 0;
+                // tensor-core tiles take ranks 16/32/64 in a layout whose B rows are contiguous
+                const bool tile_rank = (r == 16 || r == 32 || r == 64) && (cum_ranks || r == r_pool);
+                tall = (len >= kTallMin && contig && tile_rank) ? 1 : 0;
                 nchunk = (len + kChunkTok - 1) / kChunkTok;
                 int u = nchunk * n_sub(pad_rank(r));
                 us = tall ? 0 : u;

@@ -1,10 +1,418 @@
-// Prefill SGMV tiles for tall segments (placeholder until the tcgen05 kernel lands).
+// Prefill SGMV for tall segments: TMA-fed tcgen05 tiles with TMEM accumulators.
+//
+// A "tall" segment is a run of >= 32 consecutive token rows that share one adapter of rank 16,
+// 32 or 64 (the plan marks them); everything else stays on the BGMV kernels.  One work item is
+// (128-row tile of a tall segment, projection).  For it a CTA computes, entirely on chip,
+//
+//   phase 1   D1[128, r]    = X[128, h_in] . A^T          tcgen05.mma, M=128 N=r, K in blocks of 64
+//   convert   V = D1 as 16-bit (hi, and lo unless the intermediate is to be rounded)   -> smem
+//   phase 2   D2[128, 128]  = V . B[n0:n0+128, :]^T        per 128-column slice of the output
+//   epilogue  y[rows, n0:n0+128] += scale * D2
+//
+// Warp roles: warp 0 issues TMA tensor copies (x and A boxes for phase 1, B boxes for phase 2)
+// into mbarrier-tracked rings; warp 1 allocates TMEM and has one thread issue every
+// tcgen05.mma, releasing ring slots and publishing accumulators with tcgen05.commit; warps 2..5
+// read accumulators with tcgen05.ld (each warp its own 32-lane quadrant of TMEM) and do the
+// conversion and the y update.  Operand tiles use the 128/64/32-byte swizzled K-major layouts
+// that TMA writes and the MMA descriptors name.  Two D2 buffers let the MMA of slice n+1 overlap
+// the epilogue of slice n.  Single-CTA launch; every copy reads this GPU's own memory.
+//
+// Every mbarrier wait is bounded: on expiry the thread records an error word in the workspace
+// and carries on with unchanged control flow, so the kernel terminates and TMEM is released.
+//
+// Semantics: the reference's prefill op bmm(bmm(x, A^T), B^T) (lightllm/models/lora_gpu.py:127-128)
+// generalised to adapter-sorted segments; with B200_LORA_MID_ROUND the [T, r] intermediate is
+// rounded to the I/O type exactly as that op's fp16 tensors do.
 #include "lora_common.cuh"
 
 namespace b200lora {
 
-bool sgmv_tiles_supported(const ApplyParams&) { return false; }
+namespace {
 
-cudaError_t launch_sgmv_tiles(const ApplyParams&, int, int, cudaStream_t) { return cudaSuccess; }
+constexpr int kBM = 128;            // token rows per tile
+constexpr int kBK = 64;             // k columns per phase-1 block (one 128-byte swizzle atom)
+constexpr int kBN = 128;            // output columns per phase-2 slice
+constexpr int kS1 = 4;              // phase-1 ring slots
+constexpr int kS2 = 2;              // phase-2 ring slots
+constexpr int kXTile = kBM * kBK * 2;            // 16 KB
+constexpr int kATile = 64 * kBK * 2;             // 8 KB (rank 64)
+constexpr int kStage1 = kXTile + kATile;
+constexpr int kBTile = kBN * 64 * 2;             // 16 KB (rank 64)
+constexpr int kVTile = kBM * 64 * 2;             // 16 KB
+constexpr int kSmemTiles = kS1 * kStage1 + kS2 * kBTile + 2 * kVTile;
+constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 4 + 4;
+constexpr int kSgmvSmem = kSmemTiles + kNumBars * 8 + 64 + 1024;     // + alignment slack
+constexpr int kSgmvThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kD1Col = 0, kD2Col = 64;
+constexpr unsigned kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(unsigned bar, unsigned parity, unsigned* err, unsigned code) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return;
+        if ((i & 0x3fffu) == 0x3fffu && *reinterpret_cast<volatile unsigned*>(err) != 0u) break;
+    }
+    atomicMax(err, code);
+}
+__device__ __forceinline__ void tensor_g2s_2d(unsigned dst, const void* tmap, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// ---- tcgen05 wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
+                                           unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major shared-memory operand descriptor.  layout: 2 = 128-byte, 4 = 64-byte, 6 = 32-byte swizzle;
+// sbo = bytes between 8-row groups.
+__device__ __forceinline__ unsigned long long make_desc(unsigned saddr, unsigned layout, unsigned sbo) {
+    unsigned long long d = (unsigned long long)((saddr >> 4) & 0x3fffu);
+    d |= 1ull << 16;                                         // leading byte offset: unused with swizzle
+    d |= (unsigned long long)((sbo >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;                                         // descriptor version of this architecture
+    d |= (unsigned long long)layout << 61;
+    return d;
+}
+// kind::f16 instruction descriptor: fp32 accumulate, both operands K-major
+__device__ __forceinline__ unsigned make_idesc(bool bf16, int M, int N) {
+    const unsigned fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
+}
+
+struct TileInfo {
+    int adapter, rank, row0, valid, cls;     // cls: 0 -> 16, 1 -> 32, 2 -> 64
+    float scale;
+    long long a_row0;                        // first row of the A block in the [rows, h_in] view
+    long long b_row0;                        // first row of the B block in the [rows, rank] view
+};
+
+__device__ __forceinline__ TileInfo tile_info(const SgmvParams& sp, const ApplyParams& p, const PlanView& pv,
+                                              int tile, int proj) {
+    TileInfo t;
+    const int e = pv.tile_tab[tile];
+    const int seg = e >> 12, mt = e & 0xfff;
+    const int b = pv.seg_start[seg], en = pv.seg_start[seg + 1];
+    t.adapter = pv.seg_adapter[seg];
+    t.rank = pv.seg_rank[seg];
+    t.row0 = pv.perm[b] + mt * kBM;
+    t.valid = min(kBM, (en - b) - mt * kBM);
+    t.cls = t.rank == 16 ? 0 : t.rank == 32 ? 1 : 2;
+    t.scale = p.scalings ? p.scalings[t.adapter] : p.scale;
+    t.a_row0 = block_row0(p, t.adapter, t.rank);
+    // B block [h_out, rank] starts at element a_row0 * h_out; in the [rows, rank] view that is row
+    // a_row0 * (h_out / rank) (h_out is a multiple of 64).  Dense pools have rank == R.
+    t.b_row0 = p.packed ? t.a_row0 * (long long)(p.proj[proj].h_out / t.rank)
+                        : ((long long)t.adapter * p.n_layers + p.layer) * p.proj[proj].h_out;
+    (void)sp;
+    return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSgmvThreads, 1)
+sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ SgmvParams sp) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* stage1 = smem;
+    unsigned char* stage2 = smem + kS1 * kStage1;
+    unsigned char* vhi = stage2 + kS2 * kBTile;
+    unsigned char* vlo = vhi + kVTile;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(vlo + kVTile);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + kNumBars);
+    // barrier indices
+    const int FULL1 = 0, EMPTY1 = kS1, FULL2 = 2 * kS1, EMPTY2 = 2 * kS1 + kS2;
+    const int D1_FULL = 2 * kS1 + 2 * kS2, D1_EMPTY = D1_FULL + 1, V_READY = D1_FULL + 2, V_FREE = D1_FULL + 3;
+    const int D2_FULL = D1_FULL + 4, D2_EMPTY = D1_FULL + 6;
+    auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
+    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
+    const PlanHeader hdr = *pv.hdr;
+    unsigned* err = &ws.ctl->error;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_tiles = (hdr.error || hdr.cap != p.cap) ? 0 : hdr.n_tiles;
+    const int n_items = n_tiles * p.n_proj;
+    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < kS1; ++s) { mbar_init(bar(FULL1 + s), 1); mbar_init(bar(EMPTY1 + s), 1); }
+        for (int s = 0; s < kS2; ++s) { mbar_init(bar(FULL2 + s), 1); mbar_init(bar(EMPTY2 + s), 1); }
+        mbar_init(bar(D1_FULL), 1);
+        mbar_init(bar(D1_EMPTY), 128);
+        mbar_init(bar(V_READY), 128);
+        mbar_init(bar(V_FREE), 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(bar(D2_FULL + b), 1); mbar_init(bar(D2_EMPTY + b), 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                    // one warp owns the TMEM allocation
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *reinterpret_cast<volatile unsigned*>(tmem_slot);
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        unsigned n1 = 0, n2 = 0;        // ring uses so far
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int proj = item / n_tiles, tile = item - proj * n_tiles;
+            const TileInfo t = tile_info(sp, p, pv, tile, proj);
+            const ProjArgs& pj = p.proj[proj];
+            const int nkb = pj.h_in / kBK;
+            const int n_abox = t.rank / 8;
+            for (int kb = 0; kb < nkb; ++kb, ++n1) {
+                const int s = n1 % kS1;
+                mbar_wait(bar(EMPTY1 + s), ((n1 / kS1) & 1) ^ 1, err, 11);
+                const unsigned dst = smem_u32(stage1 + s * kStage1);
+                if (lane == 0) mbar_arrive_expect_tx(bar(FULL1 + s), kXTile + t.rank * kBK * 2);
+                __syncwarp();
+                // one instruction: lane 8 the x box [64 x 128], lanes 0..7 the A boxes [64 x 8]
+                if (lane == 8)
+                    tensor_g2s_2d(dst, &sp.xmap[proj], kb * kBK, t.row0, bar(FULL1 + s));
+                else if (lane < n_abox)
+                    tensor_g2s_2d(dst + kXTile + lane * 1024, &sp.amap[proj], kb * kBK, (int)t.a_row0 + lane * 8,
+                                  bar(FULL1 + s));
+            }
+            const int nnt = (pj.h_out + kBN - 1) / kBN;
+            for (int nt = 0; nt < nnt; ++nt, ++n2) {
+                const int s = n2 % kS2;
+                mbar_wait(bar(EMPTY2 + s), ((n2 / kS2) & 1) ^ 1, err, 12);
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar(FULL2 + s), kBN * t.rank * 2);
+                    tensor_g2s_2d(smem_u32(stage2 + s * kBTile), &sp.bmap[proj][t.cls], 0, (int)t.b_row0 + nt * kBN,
+                                  bar(FULL2 + s));
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        unsigned n1 = 0, n2 = 0, nd = 0, n_item = 0;
+        const bool bf16 = Cvt<T>::is_bf16;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
+            const int proj = item / n_tiles, tile = item - proj * n_tiles;
+            const TileInfo t = tile_info(sp, p, pv, tile, proj);
+            const ProjArgs& pj = p.proj[proj];
+            const int nkb = pj.h_in / kBK;
+            // phase 1: D1 = X . A^T     (D1 must have been drained by the epilogue of the previous item)
+            mbar_wait(bar(D1_EMPTY), (n_item & 1) ^ 1, err, 13);
+            tc_fence_after();
+            const unsigned idesc1 = make_idesc(bf16, kBM, t.rank);
+            for (int kb = 0; kb < nkb; ++kb, ++n1) {
+                const int s = n1 % kS1;
+                mbar_wait(bar(FULL1 + s), (n1 / kS1) & 1, err, 14);
+                tc_fence_after();
+                if (lane == 0) {
+                    const unsigned xa = smem_u32(stage1 + s * kStage1), aa = xa + kXTile;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        tc_mma_f16(tmem + kD1Col, make_desc(xa + k * 32, 2, 1024), make_desc(aa + k * 32, 2, 1024),
+                                   idesc1, (kb | k) != 0);
+                    tc_commit(bar(EMPTY1 + s));                       // slot reusable once these MMAs finish
+                    if (kb == nkb - 1) tc_commit(bar(D1_FULL));
+                }
+                __syncwarp();
+            }
+            // phase 2: D2[buf] = V . B_slice^T
+            mbar_wait(bar(V_READY), n_item & 1, err, 15);
+            tc_fence_after();
+            const unsigned layout = t.cls == 2 ? 2u : t.cls == 1 ? 4u : 6u;
+            const unsigned sbo = 8u * t.rank * 2u;
+            const unsigned idesc2 = make_idesc(bf16, kBM, kBN);
+            const int nnt = (pj.h_out + kBN - 1) / kBN;
+            for (int nt = 0; nt < nnt; ++nt, ++n2, ++nd) {
+                const int s = n2 % kS2, buf = nd & 1;
+                mbar_wait(bar(FULL2 + s), (n2 / kS2) & 1, err, 16);
+                mbar_wait(bar(D2_EMPTY + buf), ((nd >> 1) & 1) ^ 1, err, 17);
+                tc_fence_after();
+                if (lane == 0) {
+                    const unsigned ba = smem_u32(stage2 + s * kBTile);
+                    const unsigned d2 = tmem + kD2Col + buf * kBN;
+                    const int ksteps = t.rank / 16;
+                    for (int k = 0; k < ksteps; ++k)
+                        tc_mma_f16(d2, make_desc(smem_u32(vhi) + k * 32, layout, sbo), make_desc(ba + k * 32, layout, sbo),
+                                   idesc2, k != 0);
+                    if (!mid_round)
+                        for (int k = 0; k < ksteps; ++k)
+                            tc_mma_f16(d2, make_desc(smem_u32(vlo) + k * 32, layout, sbo),
+                                       make_desc(ba + k * 32, layout, sbo), idesc2, 1u);
+                    tc_commit(bar(EMPTY2 + s));
+                    tc_commit(bar(D2_FULL + buf));
+                    if (nt == nnt - 1) tc_commit(bar(V_FREE));        // V may be overwritten after this
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ================= epilogue warps =================
+        const int quad = warp & 3;                          // TMEM lanes 32*quad .. +31
+        const int row = quad * 32 + lane;
+        const unsigned lane_base = (unsigned)(quad * 32) << 16;
+        unsigned nd = 0, n_item = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
+            const int proj = item / n_tiles, tile = item - proj * n_tiles;
+            const TileInfo t = tile_info(sp, p, pv, tile, proj);
+            const ProjArgs& pj = p.proj[proj];
+            // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes
+            mbar_wait(bar(D1_FULL), n_item & 1, err, 18);
+            tc_fence_after();
+            float d1[64];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (c * 16 < t.rank) {
+                    float v[16];
+                    tc_ld16(tmem + lane_base + kD1Col + c * 16, v);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) d1[c * 16 + i] = v[i];
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(D1_EMPTY));
+            mbar_wait(bar(V_FREE), (n_item & 1) ^ 1, err, 19);       // previous item's phase 2 finished with V
+            {
+                const int rb = t.rank * 2;                            // row bytes: 32, 64, 128
+                const int sw = t.cls == 2 ? (row & 7) : t.cls == 1 ? ((row >> 1) & 3) : ((row >> 2) & 1);
+                unsigned char* rh = vhi + (row >> 3) * (8 * rb) + (row & 7) * rb;
+                unsigned char* rl = vlo + (row >> 3) * (8 * rb) + (row & 7) * rb;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (c * 8 < t.rank) {
+                        uint4 h, l;
+                        unsigned* hp = reinterpret_cast<unsigned*>(&h);
+                        unsigned* lp = reinterpret_cast<unsigned*>(&l);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = d1[c * 8 + 2 * i], b = d1[c * 8 + 2 * i + 1];
+                            const float ha = Cvt<T>::round1(a), hb = Cvt<T>::round1(b);
+                            hp[i] = Cvt<T>::pack2(ha, hb);
+                            lp[i] = Cvt<T>::pack2(a - ha, b - hb);
+                        }
+                        *reinterpret_cast<uint4*>(rh + ((c ^ sw) << 4)) = h;
+                        if (!mid_round) *reinterpret_cast<uint4*>(rl + ((c ^ sw) << 4)) = l;
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> tensor-core reads
+            mbar_arrive(bar(V_READY));
+            // ---- D2 slices -> y
+            const int nnt = (pj.h_out + kBN - 1) / kBN;
+            const bool live = row < t.valid;
+            for (int nt = 0; nt < nnt; ++nt, ++nd) {
+                const int buf = nd & 1;
+                mbar_wait(bar(D2_FULL + buf), (nd >> 1) & 1, err, 20);
+                tc_fence_after();
+#pragma unroll 2
+                for (int c = 0; c < kBN / 16; ++c) {
+                    float v[16];
+                    tc_ld16(tmem + lane_base + kD2Col + buf * kBN + c * 16, v);
+                    const int col = nt * kBN + c * 16;
+                    if (live && col < pj.h_out) {
+                        if (p.y_f32) {
+                            float4* yp = reinterpret_cast<float4*>(reinterpret_cast<float*>(pj.y) +
+                                                                   (long long)(t.row0 + row) * pj.ldy + col);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                float4 yv = yp[q];
+                                yv.x += t.scale * v[4 * q]; yv.y += t.scale * v[4 * q + 1];
+                                yv.z += t.scale * v[4 * q + 2]; yv.w += t.scale * v[4 * q + 3];
+                                yp[q] = yv;
+                            }
+                        } else {
+                            uint4* yp = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) +
+                                                                 (long long)(t.row0 + row) * pj.ldy + col);
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                uint4 yv = yp[q];
+                                float f[8];
+                                Cvt<T>::unpack8(yv, f);
+                                yv.x = Cvt<T>::pack2(f[0] + t.scale * v[8 * q], f[1] + t.scale * v[8 * q + 1]);
+                                yv.y = Cvt<T>::pack2(f[2] + t.scale * v[8 * q + 2], f[3] + t.scale * v[8 * q + 3]);
+                                yv.z = Cvt<T>::pack2(f[4] + t.scale * v[8 * q + 4], f[5] + t.scale * v[8 * q + 5]);
+                                yv.w = Cvt<T>::pack2(f[6] + t.scale * v[8 * q + 6], f[7] + t.scale * v[8 * q + 7]);
+                                yp[q] = yv;
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(bar(D2_EMPTY + buf));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+}  // namespace
+
+bool sgmv_tiles_supported(const ApplyParams& p) {
+    for (int i = 0; i < p.n_proj; ++i)
+        if ((p.proj[i].h_in % kBK) || (p.proj[i].h_out % 64)) return false;
+    return true;
+}
+
+cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io_dtype, int n_sm, cudaStream_t s) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(sgmv_tile_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSgmvSmem);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(sgmv_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSgmvSmem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    if (io_dtype == B200_LORA_F16) sgmv_tile_kernel<__half><<<n_sm, kSgmvThreads, kSgmvSmem, s>>>(p, sp);
+    else sgmv_tile_kernel<__nv_bfloat16><<<n_sm, kSgmvThreads, kSgmvSmem, s>>>(p, sp);
+    return cudaGetLastError();
+}
 
 }  // namespace b200lora

@@ -148,7 +148,8 @@ def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan:
                       x.stride(0), y.stride(0), pool.h_in, pool.h_out)
     ad = adapters if adapters is not None else adapters_of(projs[0][2])
     check(_lib.lib().b200_lora_apply(
-        arr, len(projs), C.byref(ad), plan.buf.data_ptr(), plan.max_tokens, int(layer), _DT[io], _DT[ydt],
+        arr, len(projs), C.byref(ad), plan.buf.data_ptr(), plan.max_tokens, int(projs[0][0].shape[0]), int(layer),
+        _DT[io], _DT[ydt],
         int(flags), workspace.buf.data_ptr(), workspace.nbytes, _stream(projs[0][0].device)), "apply")
 
 
@@ -207,16 +208,23 @@ class LoraBatch:
     def __init__(self, max_tokens: int, n_adapters: int, max_h_in: int, n_proj: int = 4, device="cuda"):
         self.plan = LoraPlan(max_tokens, n_adapters, device)
         self.workspace = LoraWorkspace(max_tokens, n_proj, max_h_in, device)
+        self.tiles = False
 
-    def set_ids(self, ids: torch.Tensor, pool: AdapterPool) -> "LoraBatch":
+    def set_ids(self, ids: torch.Tensor, pool: AdapterPool, tiles: bool = False) -> "LoraBatch":
+        """Per-token adapter ids.  ``tiles=True`` also launches the tcgen05 tile kernel for
+        tall contiguous runs (mixed prefill + decode batches); decode batches leave it off."""
         self.plan.build(ids, adapters_of(pool))
+        self.tiles = tiles
         return self
 
-    def set_segments(self, seg_starts, seg_adapter, n_tokens, pool: AdapterPool) -> "LoraBatch":
+    def set_segments(self, seg_starts, seg_adapter, n_tokens, pool: AdapterPool, tiles: bool = True) -> "LoraBatch":
         self.plan.from_segments(seg_starts, seg_adapter, n_tokens, adapters_of(pool))
+        self.tiles = tiles
         return self
 
     def apply(self, projs, layer: int, flags: int = 0) -> None:
+        if not self.tiles:
+            flags |= _lib.NO_TENSOR
         apply(projs, self.plan, layer, self.workspace, flags)
 
 

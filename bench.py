@@ -144,14 +144,17 @@ def main():
     batch = L.LoraBatch(T, wl.n_adapters, wl.projections[0].h_in, 3, dev)
     stream = torch.cuda.Stream(dev)
 
+    # prompts (runs of >= 32 rows of one adapter) go to the tcgen05 tile kernel
+    use_tiles = wl.seq_lens is not None
+
     def one_pass(flags=0, plan=True):
         if plan:
-            batch.set_ids(ids, pools["q"])
+            batch.set_ids(ids, pools["q"], tiles=use_tiles)
         for l in range(n_layers):
             batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l, flags)
             batch.apply([(x_o[l], ys["o"][l], pools["o"])], l, flags)
 
-    launches_per_pass = 1 + n_layers * 4
+    launches_per_pass = 1 + n_layers * (6 if use_tiles else 4)
 
     def capture(flags=0, plan=True):
         g = torch.cuda.CUDAGraph()
@@ -167,7 +170,7 @@ def main():
         with torch.cuda.stream(stream):
             with torch.cuda.graph(g, stream=stream):
                 for _ in range(8):
-                    batch.set_ids(ids, pools["q"])
+                    batch.set_ids(ids, pools["q"], tiles=use_tiles)
         return g
 
     def timed(graph, steps, warmup):
@@ -237,7 +240,7 @@ def main():
         def e2e_step():
             with torch.cuda.stream(stream):
                 ids.copy_(ids_host, non_blocking=True)
-                batch.set_ids(ids, pools["q"])
+                batch.set_ids(ids, pools["q"], tiles=use_tiles)
             ev_in, ev_done = [], []
             with torch.cuda.stream(copy_in):
                 for l in range(n_layers):

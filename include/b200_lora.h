@@ -123,11 +123,14 @@ size_t b200_lora_workspace_bytes(int32_t max_tokens, int32_t n_proj, int32_t max
 int b200_lora_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Applies the delta of `layer` to up to B200_LORA_MAX_PROJ projections in one pass.
- * io_dtype: type of x, wa, wb (F16 | BF16).  y_dtype: io_dtype or F32. */
+ * io_dtype: type of x, wa, wb (F16 | BF16).  y_dtype: io_dtype or F32.  n_tokens: rows of x
+ * and y (the value the plan was built with).  Unless B200_LORA_NO_TENSOR is set, tall
+ * contiguous segments of rank 16/32/64 run on the tcgen05 tile kernel, the rest on the BGMV
+ * kernels; decode-only batches should set the flag and save that kernel's launch. */
 int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
-                    const void* plan, int32_t max_tokens, int32_t layer, int32_t io_dtype,
-                    int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes,
-                    void* stream);
+                    const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer,
+                    int32_t io_dtype, int32_t y_dtype, int32_t flags, void* workspace,
+                    size_t workspace_bytes, void* stream);
 
 /* Reads the workspace's sticky device-side error word (synchronises `stream`):
  * B200_LORA_OK, or B200_LORA_ERR_TIMEOUT if a bounded wait inside a kernel expired. */

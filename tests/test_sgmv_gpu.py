@@ -1,0 +1,118 @@
+"""GPU parity of the prefill SGMV path (tcgen05 tiles for tall segments + BGMV for the rest)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import ae296_b200 as L
+from lora_testlib import TOL, Case, rel_err
+from oracle import lora_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def seg_case(lens, adapters, ranks, n_adapters, h_in, h_out, dtype="fp16", dense=False, seed=0):
+    ids = np.repeat(np.asarray(adapters, np.int32), lens)
+    c = Case(int(np.sum(lens)), n_adapters, h_in, h_out, np.asarray(ranks, np.int32), dtype, dense=dense, seed=seed, ids=ids)
+    starts = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    c.seg_starts = torch.from_numpy(starts).cuda()
+    c.seg_adapter = torch.from_numpy(np.asarray(adapters, np.int32)).cuda()
+    return c
+
+
+def run_segments(c, layer, y_dtype=None, flags=0, tiles=True):
+    y = torch.zeros(c.T, c.h_out, dtype=c.tdt if y_dtype is None else y_dtype, device="cuda")
+    batch = L.LoraBatch(c.T, c.N, c.h_in, 1)
+    batch.set_segments(c.seg_starts, c.seg_adapter, c.T, c.pool, tiles=tiles)
+    batch.apply([(c.x, y, c.pool)], layer, flags)
+    torch.cuda.synchronize()
+    batch.workspace.check()
+    return y
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_tall_and_short_segments_mixed_ranks(dtype):
+    # tall tiles: ranks 16/32/64 with >= 32 rows (one spans two tiles, one ends mid-tile);
+    # BGMV: the rank-8 segment, the 5-row and the 31-row segments
+    lens = [5, 200, 37, 130, 31, 64, 128, 40]
+    adapters = [0, 1, 2, 3, 4, 5, 6, 7]
+    ranks = [16, 64, 32, 16, 64, 8, 32, 64]
+    c = seg_case(lens, adapters, ranks, 8, 512, 384, dtype, seed=17)
+    for layer in (0, 1):
+        want = c.oracle_delta(layer)
+        y32 = run_segments(c, layer, y_dtype=torch.float32)
+        assert rel_err(y32.double().cpu().numpy(), want) <= TOL
+        # the same batch entirely on the BGMV kernels agrees too
+        y32b = run_segments(c, layer, y_dtype=torch.float32, tiles=False)
+        assert rel_err(y32b.double().cpu().numpy(), want) <= TOL
+        # 16-bit output: one rounding of the fp32 result
+        y16 = run_segments(c, layer)
+        assert torch.equal(y16, y32.to(c.tdt))
+        assert torch.equal(run_segments(c, layer, y_dtype=torch.float32), y32)      # reproducible
+
+
+def test_mid_round_matches_rounded_intermediate():
+    c = seg_case([96, 33, 140], [2, 0, 1], [32, 16, 64], 3, 256, 256, "fp16", seed=5)
+    y32 = run_segments(c, 1, y_dtype=torch.float32, flags=L.MID_ROUND)
+    assert rel_err(y32.double().cpu().numpy(), c.oracle_delta(1, mid_round="fp16")) <= TOL
+
+
+def test_reference_prefill_golden():
+    """The reference's own prefill method (two fp16 batched matmuls) on its own inputs."""
+    g = np.load(os.path.join(GOLD, "prefill_bmm_small.npz"))
+    B, Lp, H, r, nl, layer = [int(v) for v in g["dims"]]
+    x = torch.from_numpy(g["x"]).cuda().reshape(B * Lp, H)
+    wa, wb = torch.from_numpy(g["wa"]).cuda(), torch.from_numpy(g["wb"]).cuda()
+    pool = L.AdapterPool(wa, wb, None, None, None, B, nl, H, H, r, False, np.full(B, r, np.int32),
+                         np.arange(B + 1, dtype=np.int64) * r)
+    ad = L.ops._adapters_struct(B, nl, r)
+    batch = L.LoraBatch(B * Lp, B, H, 1)
+    starts = torch.arange(0, (B + 1) * Lp, Lp, dtype=torch.int32, device="cuda")
+    batch.plan.from_segments(starts, torch.arange(B, dtype=torch.int32, device="cuda"), B * Lp, ad)
+    y = torch.zeros(B * Lp, H, dtype=torch.float16, device="cuda")
+    L.apply([(x, y, pool)], batch.plan, layer, batch.workspace, L.MID_ROUND, ad)
+    torch.cuda.synchronize()
+    batch.workspace.check()
+    ref = g["y"].astype(np.float64).reshape(B * Lp, H)
+    got = y.double().cpu().numpy()
+    rms = np.sqrt((ref ** 2).mean())
+    # both sides round the intermediate and the output to fp16: allow one output ulp on top
+    assert np.abs(got - ref).max() <= TOL * rms + np.abs(ref).max() * 2 ** -10
+
+
+def test_lora_gpu_mirror_prefill_and_decode():
+    cfg = {"n_layers": 2, "batch_size": 8, "lora_rank": 16, "hidden_dim": 256, "tp_degree": 1,
+           "max_prefill_batch_size": 3, "mode": "aaas-cached"}
+    torch.manual_seed(0)
+    obj = L.Lora_GPU(cfg)
+    x = torch.randn(3, 40, 256, device="cuda").half()
+    y = obj.invoke_one_layer_q(x, 1, prefill=True)
+    ref = O.prefill_bmm(x, obj.q_down_prefill[:3, 1], obj.q_up_prefill[:3, 1])
+    rms = float(ref.float().pow(2).mean().sqrt())
+    assert float((y.float() - ref.float()).abs().max()) <= TOL * rms + float(ref.abs().max()) * 2 ** -10
+    xd = torch.randn(5, 256, device="cuda").half()
+    idx = torch.tensor([3, 0, 7, 3, 1], device="cuda")
+    obj.set_indices(idx)
+    yd = obj.invoke_one_layer_k(xd, 0)
+    want = torch.stack([(xd[i].float() @ obj.k_down[idx[i], 0].float().t()) @ obj.k_up[idx[i], 0].float().t()
+                        for i in range(5)])
+    rms = float(want.pow(2).mean().sqrt())
+    assert float((yd.float() - want).abs().max()) <= TOL * rms + float(want.abs().max()) * 2 ** -10
+
+
+def test_mixed_decode_and_prefill_from_ids():
+    """Per-token ids: decode tokens in random order followed by contiguous prompts."""
+    rng = np.random.default_rng(3)
+    n = 12
+    ranks = rng.choice([16, 32, 64], n).astype(np.int32)
+    dec = rng.integers(0, n, 70)
+    ids = np.concatenate([dec, np.repeat([11, 4], [150, 64])]).astype(np.int32)   # adapter 4 may also decode
+    c = Case(len(ids), n, 512, 512, ranks, "bf16", seed=23, ids=ids)
+    y = torch.zeros(c.T, c.h_out, dtype=torch.float32, device="cuda")
+    batch = L.LoraBatch(c.T, n, 512, 1).set_ids(c.ids_dev, c.pool, tiles=True)
+    batch.apply([(c.x, y, c.pool)], 0)
+    torch.cuda.synchronize()
+    batch.workspace.check()
+    assert rel_err(y.double().cpu().numpy(), c.oracle_delta(0)) <= TOL
