@@ -324,4 +324,46 @@ int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void*
                            workspace_bytes_ - pb, stream);
 }
 
+// ---- allocation-free variant ---------------------------------------------------------------
+// Scratch for b200_add_lora_bgmv_static: plan + workspace of the largest accepted call.  It
+// lives in the library image, so every GPU that loads the library carries it until exit.
+__device__ __align__(256) unsigned char g_static_scratch[B200_LORA_STATIC_SCRATCH_BYTES];
+
+int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, const void* wb_T_all,
+                              const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
+                              int32_t h_in, int32_t h_out, int32_t n_adapters, int32_t n_layers, int32_t r,
+                              int32_t layer_idx, float scale, int32_t dtype, void* stream) {
+    if (n_tokens < 1 || n_tokens > B200_LORA_STATIC_MAX_TOKENS || n_adapters < 1 ||
+        n_adapters > B200_LORA_STATIC_MAX_ADAPTERS || h_in < 8 || h_in > B200_LORA_STATIC_MAX_H_IN)
+        return B200_LORA_ERR_WORKSPACE;          // beyond what the static scratch was sized for
+    const size_t need = b200_add_lora_bgmv_workspace_bytes(n_tokens, n_adapters, h_in);
+    if (need == 0 || need > (size_t)B200_LORA_STATIC_SCRATCH_BYTES) return B200_LORA_ERR_WORKSPACE;
+
+    // One-time set-up per device: in host code `g_static_scratch` is only a stand-in for the
+    // device array, so its device address has to be asked for, with that device current.
+    static void* dev_ptr[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev < 0 || dev >= 64) return B200_LORA_ERR_UNSUPPORTED;
+    if (!dev_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e);
+        dev_ptr[dev] = ptr;
+    }
+    void* scratch = dev_ptr[dev];
+    // The array keeps whatever the previous call left.  The kernels need their control words
+    // (tickets, arrival counters, slot masks, error word) to start at zero: clear that prefix
+    // of the workspace part; the plan part is rebuilt from scratch by every call.
+    const size_t pb = (b200_lora_plan_bytes(n_tokens, n_adapters) + 255) & ~size_t(255);
+    const size_t ctl_bytes = sizeof(WorkspaceCtl) + 4 * ((ws_counter_words(n_tokens) + 3) & ~size_t(3)) +
+                             8 * ws_counter_words(n_tokens);
+    e = cudaMemsetAsync(static_cast<char*>(scratch) + pb, 0, ctl_bytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e);
+    return b200_add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, indicies_are_i64, n_tokens, h_in, h_out,
+                              n_adapters, n_layers, r, layer_idx, scale, dtype, scratch,
+                              (size_t)B200_LORA_STATIC_SCRATCH_BYTES, stream);
+}
+
 }  // extern "C"

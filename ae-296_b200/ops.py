@@ -202,6 +202,37 @@ def add_lora_bgmv(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T
         _DT[x.dtype], ws.data_ptr(), ws.numel() * 8, _stream(x.device)), "add_lora_bgmv")
 
 
+def add_lora_bgmv_static(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T_all: torch.Tensor,
+                         indicies: torch.Tensor, layer_idx: int, scale: float) -> None:
+    """``add_lora_bgmv`` for callers that must not allocate device memory.
+
+    Same arguments and result as :func:`add_lora_bgmv`, but the library's built-in scratch
+    array is used instead of a workspace tensor, so nothing is allocated - not by this wrapper
+    either.  Meant for processes that have given all of HBM to their KV cache or that may not
+    call ``cudaMalloc`` after start-up.  Accepts at most 64 tokens, 1024 adapters and
+    ``h_in <= 8192`` (larger calls raise).  All calls on a GPU share that one array: issue them
+    on one stream, or order the streams, because overlapping calls race.  Make the first call
+    on a device outside stream capture (it performs a one-time address lookup)."""
+    _require_cuda(y, x, wa_T_all, wb_T_all, indicies)
+    n, l, r, h_in = wa_T_all.shape
+    h_out = wb_T_all.shape[2]
+    t = x.shape[0]
+    if tuple(wb_T_all.shape) != (n, l, h_out, r) or tuple(x.shape) != (t, h_in) or tuple(y.shape) != (t, h_out) \
+            or indicies.numel() != t:
+        raise ValueError("x, y, indicies shapes disagree with the pools")
+    for ten in (y, x, wa_T_all, wb_T_all, indicies):
+        if not ten.is_contiguous():
+            raise ValueError("add_lora_bgmv_static needs contiguous tensors")
+    if not (y.dtype == x.dtype == wa_T_all.dtype == wb_T_all.dtype) or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("fp16 or bf16 tensors of one dtype expected")
+    if indicies.dtype not in (torch.int32, torch.int64):
+        raise ValueError("indicies must be int32 or int64")
+    check(_lib.lib().b200_add_lora_bgmv_static(
+        y.data_ptr(), x.data_ptr(), wa_T_all.data_ptr(), wb_T_all.data_ptr(), indicies.data_ptr(),
+        1 if indicies.dtype == torch.int64 else 0, t, h_in, h_out, n, l, r, int(layer_idx), float(scale),
+        _DT[x.dtype], _stream(x.device)), "add_lora_bgmv_static")
+
+
 class LoraBatch:
     """Plan + workspace of one batch, reused across layers and projections."""
 

@@ -148,6 +148,34 @@ int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void*
                        int32_t layer_idx, float scale, int32_t dtype,
                        void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- allocation-free variant of the operator call ------------------------------------------
+ * No counterpart in the reference.  Some callers may not allocate device memory at all: a
+ * serving process that has already handed every free byte of HBM to its KV cache (a late
+ * cudaMalloc would fail or evict), a decode loop that cannot afford the device-wide
+ * synchronisation cudaMalloc/cudaFree imply, or a host whose policy forbids allocation after
+ * start-up.  For them this entry point takes only inputs and outputs; the
+ * plan and the split-K scratch that b200_add_lora_bgmv keeps in a caller-provided workspace
+ * live in a fixed array inside the library (B200_LORA_STATIC_SCRATCH_BYTES, present on every
+ * GPU that loads the library, for the life of the process).  It calls no cudaMalloc, cudaFree
+ * or allocating library routine.
+ *
+ * Limits: n_tokens <= B200_LORA_STATIC_MAX_TOKENS, n_adapters <= B200_LORA_STATIC_MAX_ADAPTERS,
+ * h_in <= B200_LORA_STATIC_MAX_H_IN; anything larger returns B200_LORA_ERR_WORKSPACE and does
+ * nothing.  The first call on a device looks up the array's device address (one-time set-up),
+ * so make that first call outside any stream capture.  All calls on one GPU share the one
+ * array: calls that may overlap on the GPU (different streams without an ordering between
+ * them) race on it and give wrong results; calls ordered on one stream are fine. */
+enum {
+    B200_LORA_STATIC_MAX_TOKENS = 64,
+    B200_LORA_STATIC_MAX_ADAPTERS = 1024,
+    B200_LORA_STATIC_MAX_H_IN = 8192,
+    B200_LORA_STATIC_SCRATCH_BYTES = 3 * 512 * 1024
+};
+int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, const void* wb_T_all,
+                              const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
+                              int32_t h_in, int32_t h_out, int32_t n_adapters, int32_t n_layers, int32_t r,
+                              int32_t layer_idx, float scale, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
