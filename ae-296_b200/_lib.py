@@ -55,6 +55,7 @@ SYMBOLS = {
                                       C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_void_p]),
     "b200_lora_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "b200_lora_workspace_init": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200_lora_workspace_v_region": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "b200_lora_workspace_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b200_lora_apply": (C.c_int, [C.POINTER(Proj), C.c_int32, C.POINTER(Adapters), C.c_void_p, C.c_int32,
                                   C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,

@@ -124,6 +124,10 @@ PlanAdapters plan_adapters(const b200_lora_adapters* ad) {
 
 }  // namespace
 
+// Scratch for b200_add_lora_bgmv_static: plan + workspace of the largest accepted call.  It
+// lives in the library image, so every GPU that loads the library carries it until exit.
+static __device__ __align__(256) unsigned char g_static_scratch[B200_LORA_STATIC_SCRATCH_BYTES];
+
 extern "C" {
 
 int b200_lora_arch(void) { return 100; }
@@ -285,6 +289,16 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }
 
+int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* offset_bytes, size_t* size_bytes) {
+    if (!offset_bytes || !size_bytes) return B200_LORA_ERR_NULL;
+    if (max_tokens < 1 || n_proj < 1 || n_proj > kMaxProj) return B200_LORA_ERR_DIM;
+    // the view only does address arithmetic: run it on a fictitious 128-byte-aligned base
+    WorkspaceView w = workspace_view(reinterpret_cast<void*>(uintptr_t(1) << 20), max_tokens, n_proj);
+    *offset_bytes = reinterpret_cast<uintptr_t>(w.v) - (uintptr_t(1) << 20);
+    *size_bytes = (size_t)n_proj * max_tokens * kMaxRank * 4;
+    return B200_LORA_OK;
+}
+
 int b200_lora_workspace_status(const void* workspace, void* stream) {
     if (!workspace) return B200_LORA_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -325,10 +339,6 @@ int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void*
 }
 
 // ---- allocation-free variant ---------------------------------------------------------------
-// Scratch for b200_add_lora_bgmv_static: plan + workspace of the largest accepted call.  It
-// lives in the library image, so every GPU that loads the library carries it until exit.
-__device__ __align__(256) unsigned char g_static_scratch[B200_LORA_STATIC_SCRATCH_BYTES];
-
 int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, const void* wb_T_all,
                               const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
                               int32_t h_in, int32_t h_out, int32_t n_adapters, int32_t n_layers, int32_t r,

@@ -114,8 +114,20 @@ class LoraWorkspace:
         nbytes = _lib.lib().b200_lora_workspace_bytes(self.max_tokens, self.n_proj, self.max_h_in)
         if nbytes == 0:
             raise ValueError("bad workspace dimensions")
-        self.buf = torch.zeros((nbytes + 15) // 16 * 2, dtype=torch.int64, device=device)   # zero-filled once
-        self.nbytes = self.buf.numel() * 8
+        # 128-byte aligned base: the library's layout aligns v relative to the base address
+        raw = torch.zeros(nbytes + 128, dtype=torch.uint8, device=device)                   # zero-filled once
+        skew = (-raw.data_ptr()) % 128
+        self._raw = raw
+        self.buf = raw[skew: skew + nbytes]
+        self.nbytes = nbytes
+
+    def v_view(self) -> torch.Tensor:
+        """The fp32 shrink result ``v [n_proj, max_tokens, 64]`` inside the workspace
+        (what tensor-parallel ranks sum between the shrink and the expand half)."""
+        off, size = C.c_size_t(0), C.c_size_t(0)
+        check(_lib.lib().b200_lora_workspace_v_region(self.max_tokens, self.n_proj, C.byref(off), C.byref(size)),
+              "workspace_v_region")
+        return self.buf[off.value: off.value + size.value].view(torch.float32).view(self.n_proj, self.max_tokens, 64)
 
 
 def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan: LoraPlan, layer: int,

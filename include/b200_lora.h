@@ -132,6 +132,12 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
                     int32_t io_dtype, int32_t y_dtype, int32_t flags, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* Where the fp32 shrink result v [n_proj][max_tokens][64] sits inside a workspace: byte offset
+ * and size.  Tensor-parallel callers all-reduce this region between a B200_LORA_ONLY_SHRINK
+ * and a B200_LORA_ONLY_EXPAND call (A sharded along h_in, B along h_out); the reference
+ * replicates A instead and needs no exchange (lightllm/models/lora_gpu.py:25-26,33-34). */
+int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* offset_bytes, size_t* size_bytes);
+
 /* Reads the workspace's sticky device-side error word (synchronises `stream`):
  * B200_LORA_OK, or B200_LORA_ERR_TIMEOUT if a bounded wait inside a kernel expired. */
 int b200_lora_workspace_status(const void* workspace, void* stream);
