@@ -103,6 +103,104 @@ def reference_arm(args, rank, world):
     print(json.dumps(out), flush=True)
 
 
+def tensor_parallel_arm(args, wl, rank, local, world, dev):
+    """Workloads 3 and 4 on N GPUs: A sharded along hidden, B along output, NCCL all-reduce of the
+    fp32 shrink partials between the two halves.  Total work is fixed: strong scaling."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from ae296_b200.pool import AdapterPool
+    from ae296_b200.tp import TPLora
+    from ae296_b200.workloads import SEED_BASE, torch_dtype
+
+    tp = world
+    dt = torch_dtype(wl.dtype)
+    T = wl.n_tokens
+    n_layers = args.layers or wl.n_layers
+    per_layer = wl.pool_bytes() // wl.n_layers // tp
+    free_b, _ = torch.cuda.mem_get_info()
+    fit = int((free_b * 0.8) // (per_layer + 1))
+    note = None
+    if n_layers > fit:
+        note = f"pool trimmed to {fit} of {n_layers} layers to fit"
+        n_layers = fit
+    g = torch.Generator(device=dev).manual_seed(SEED_BASE + wl.cfg + 100 * rank)
+    pools, xs, ys = {}, {}, {}
+    for p in wl.projections:
+        hi, ho = p.h_in // tp, p.h_out // tp
+        pool = AdapterPool.empty(wl.n_adapters, n_layers, hi, ho, wl.ranks, wl.scalings, dtype=dt, device=dev)
+        pool.wa.normal_(0, 1.0 / float(np.sqrt(p.h_in)), generator=g)
+        pool.wb.normal_(0, 0.15, generator=g)
+        pools[p.name] = pool
+        ys[p.name] = torch.zeros(n_layers, T, ho, dtype=dt, device=dev)
+    hi = wl.projections[0].h_in // tp
+    x_qkv = torch.empty(n_layers, T, hi, dtype=dt, device=dev).normal_(0, 1, generator=g)
+    x_o = torch.empty(n_layers, T, hi, dtype=dt, device=dev).normal_(0, 1, generator=g)
+    ids = torch.from_numpy(wl.ids).to(dev)
+    eng = TPLora(T, wl.n_adapters, hi, 3, tp, rank, None, dev)
+    names = [p.name for p in wl.projections]
+    stream = torch.cuda.Stream(dev)
+
+    def one_pass():
+        eng.set_ids(ids, pools["q"])
+        for l in range(n_layers):
+            eng.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
+            eng.apply([(x_o[l], ys["o"][l], pools["o"])], l)
+
+    mode = "cuda-graph"
+    with torch.cuda.stream(stream):
+        one_pass()
+        stream.synchronize()
+        dist.barrier()
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                one_pass()
+            run = graph.replay
+        except Exception:                       # NCCL inside a graph refused: time eager launches
+            mode = "eager"
+            run = one_pass
+        for _ in range(max(args.warmup, 3)):
+            run()
+        stream.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clk:
+            e0.record(stream)
+            for _ in range(args.steps):
+                run()
+            e1.record(stream)
+            stream.synchronize()
+        torch.cuda.synchronize()
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    tms = torch.tensor([ms], device=dev)
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    eng.batch.workspace.check()
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = json.load(open(peaks_path))["hbm_gbs"] if os.path.exists(peaks_path) else 6650.0
+        per_gpu = wl.bytes_per_layer(tp=tp) * n_layers + 2 * 4 * T * 64 * 4 * 2 * n_layers
+        out = {
+            "metric": "lora_shrink_expand_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32-accumulate/" + wl.dtype, "data": "synthetic",
+            "config": {"workload": f"cfg{wl.cfg}:{wl.name}", "tokens": T, "layers": n_layers,
+                       "adapters": wl.n_adapters, "parallelism": f"tp{tp}: A row-sharded, B column-sharded, "
+                       "NCCL all-reduce of fp32 [T,64] shrink partials", "timing": mode,
+                       "l2": "inputs larger than L2", "note": note},
+            "roofline": {"bound": "hbm", "kernel": "whole pass per GPU (shrink + all-reduce + expand)",
+                         "achieved": per_gpu / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": per_gpu / (ms * 1e-3) / 1e9 / peak, "traffic": None},
+            "cpu_baseline": None, "e2e": None,
+            "gpu_launches": (1 + n_layers * 4) * args.steps, "clocks": clk.summary(),
+        }
+        print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -125,6 +223,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     wl = make_workload(args.workload)
+    if wl.cfg in (3, 4) and world > 1:
+        tensor_parallel_arm(args, wl, rank, local, world, dev)
+        dist.destroy_process_group()
+        return
     n_layers = args.layers or wl.n_layers
     # keep the resident pool within one GPU: trim depth if the full pool would not fit
     free_b, _ = torch.cuda.mem_get_info()
