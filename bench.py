@@ -317,10 +317,14 @@ def main():
     ms_shr = timed(capture(_lib.ONLY_SHRINK, plan=False), args.steps, 3)
     us_plan = timed(capture_plan_only(), args.steps, 3) * 1e3 / 8
     n_exp_launch = n_layers * 2
+    # DRAM bytes per expand launch from the ncu capture summarised in
+    # profiles/bgmv_tma_cfg1_ncu_full.md (dram__bytes_read.sum + dram__bytes_write.sum, mean of the
+    # q/k/v and the o launch of one layer; one launch = one layer at any depth)
+    traffic = 42.25e6 if wl.cfg == 1 else None
     ach = exp_bytes / (ms_exp * 1e-3) / 1e9
     roofline = {
         "bound": "hbm", "kernel": "bgmv_expand_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
-        "frac": ach / peak, "traffic": None, "peak_source": peak_src,
+        "frac": ach / peak, "traffic": traffic, "peak_source": peak_src,
         "bytes_per_launch": exp_bytes / n_exp_launch, "us_per_launch": ms_exp * 1e3 / n_exp_launch,
         "frac_of_8TBs_nominal": ach / 8000.0,
         "shrink": {"kernel": "bgmv_shrink_kernel", "achieved": shr_bytes / (ms_shr * 1e-3) / 1e9,
