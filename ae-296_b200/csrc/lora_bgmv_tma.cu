@@ -38,10 +38,14 @@
 #define TRACE_DECL long long tr_t0 = clock64(); long long tr_acc[6] = {0, 0, 0, 0, 0, 0};
 #define TRACE_MARK(i) { long long tr_t1 = clock64(); tr_acc[i] += tr_t1 - tr_t0; tr_t0 = tr_t1; }
 #define TRACE_FLUSH(cond, base) if ((cond) && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) atomicAdd(&ws.ctl->pad[(base) + i], (unsigned)(tr_acc[i] >> 4)); }
+#define TRACE_ARGS , long long& tr_t0, long long (&tr_acc)[6]
+#define TRACE_PASS , tr_t0, tr_acc
 #else
 #define TRACE_DECL
 #define TRACE_MARK(i)
 #define TRACE_FLUSH(cond, base)
+#define TRACE_ARGS
+#define TRACE_PASS
 #endif
 
 namespace b200lora {
@@ -355,20 +359,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
     int* s_flag = reinterpret_cast<int*>(bars + 2 * kStages);
 
-    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
-    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
-    const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
-    const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
-    const int n_items = n_units * p.total_super_in;
+    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // each CTA takes a contiguous range of items
-    const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int first = blockIdx.x * per_cta;
-    if (first >= n_items) return;
-    const int n_local = min(per_cta, n_items - first);
-    unsigned* err = &ws.ctl->error;
-
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);                 // full: producer's arrive + tx bytes
@@ -377,6 +369,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait_prior();                                      // everything below may read the predecessor's output
+
+    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
+    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
+    const PlanHeader hdr = *pv.hdr;
+    if (hdr.error || hdr.cap != p.cap) return;
+    const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
+    const int n_items = n_units * p.total_super_in;
+    // each CTA takes a contiguous range of items
+    const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int first = blockIdx.x * per_cta;
+    if (first >= n_items) return;
+    const int n_local = min(per_cta, n_items - first);
+    unsigned* err = &ws.ctl->error;
 
     if (warp >= kConsWarps) {
         // ---------------- producer warps ----------------
@@ -494,7 +500,7 @@ __device__ __forceinline__ void split2(float v0, float v1, unsigned& hi, unsigne
 //   R=32: chunk t of each 64-byte row (2 k-steps);  R=16: 8 bytes (1 k-step);  R=8: 4 bytes.
 // All of a warp's MMAs are issued before any result is used.
 template <typename T, int R>
-__device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid) {
+__device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid TRACE_ARGS) {
     constexpr int CALLS = R == 64 ? 4 : R == 32 ? 2 : 1;
     constexpr int JC = kSuper / (R <= 16 ? 4 : R / 4);
     constexpr int NBW = JC / 8 / kConsWarps;               // 8-row blocks per warp: 8, 8, 4, 2
@@ -536,6 +542,7 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
         }
     }
 
+    TRACE_MARK(2)
     const int jbase = warp * NBW * 8;
     float acc[NBW][CALLS][4];
 #pragma unroll
@@ -562,6 +569,7 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
             Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], 0u, 0u, w0, 0u);
         }
     }
+    TRACE_MARK(3)
     // y[token g][j, j+1] += scale * (hi + lo products)
     unsigned char* ysb = stage + kWTile;
     constexpr int ypitch = JC * 2 + kYPad;
@@ -600,19 +608,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
     Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kExpandStage);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
 
-    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
-    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
-    const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
-    const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
-    const int n_items = n_units * p.total_super_out;
+    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int first = blockIdx.x * per_cta;
-    if (first >= n_items) return;
-    const int n_local = min(per_cta, n_items - first);
-    unsigned* err = &ws.ctl->error;
-
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);
@@ -621,6 +618,19 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    pdl_wait_prior();
+
+    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
+    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
+    const PlanHeader hdr = *pv.hdr;
+    if (hdr.error || hdr.cap != p.cap) return;
+    const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
+    const int n_items = n_units * p.total_super_out;
+    const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int first = blockIdx.x * per_cta;
+    if (first >= n_items) return;
+    const int n_local = min(per_cta, n_items - first);
+    unsigned* err = &ws.ctl->error;
 
     if (warp >= kConsWarps) {
         const int pw = warp - kConsWarps;
@@ -663,15 +673,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         unsigned char* stage = smem + s * kExpandStage;
         if (m.valid) {
             switch (m.u.rank) {
-                case 8:  expand_consume<T, 8>(p, m, stage, tid); break;
-                case 16: expand_consume<T, 16>(p, m, stage, tid); break;
-                case 32: expand_consume<T, 32>(p, m, stage, tid); break;
-                default: expand_consume<T, 64>(p, m, stage, tid); break;
+                case 8:  expand_consume<T, 8>(p, m, stage, tid TRACE_PASS); break;
+                case 16: expand_consume<T, 16>(p, m, stage, tid TRACE_PASS); break;
+                case 32: expand_consume<T, 32>(p, m, stage, tid TRACE_PASS); break;
+                default: expand_consume<T, 64>(p, m, stage, tid TRACE_PASS); break;
             }
         }
-        TRACE_MARK(2)
+        TRACE_MARK(4)
         cons_sync();
-        TRACE_MARK(3)
         if (m.valid && !p.y_f32) {
             // coalesced write-back of the updated y tile, 16 bytes per thread
             const ProjArgs& pj = p.proj[m.proj];
@@ -687,7 +696,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));     // one arrival per consumer warp
-        TRACE_MARK(4)
+        TRACE_MARK(0)
     }
     TRACE_FLUSH(tid == 0, 5)
 }
@@ -710,9 +719,11 @@ cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int grid = n_sm * kCtasPerSm;
-    if (!(p.flags & B200_LORA_ONLY_EXPAND)) bgmv_shrink_tma_kernel<T><<<grid, kThreads, kShrinkSmem, s>>>(p);
-    if (!(p.flags & B200_LORA_ONLY_SHRINK)) bgmv_expand_tma_kernel<T><<<grid, kThreads, kExpandSmem, s>>>(p);
-    return cudaGetLastError();
+    cudaError_t e = cudaSuccess;
+    if (!(p.flags & B200_LORA_ONLY_EXPAND)) e = launch_pdl(bgmv_shrink_tma_kernel<T>, grid, kThreads, kShrinkSmem, s, p);
+    if (e == cudaSuccess && !(p.flags & B200_LORA_ONLY_SHRINK))
+        e = launch_pdl(bgmv_expand_tma_kernel<T>, grid, kThreads, kExpandSmem, s, p);
+    return e;
 }
 
 }  // namespace

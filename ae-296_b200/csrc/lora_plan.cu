@@ -193,6 +193,8 @@ template <typename IdT>
 __global__ void __launch_bounds__(kPlanThreads, 1)
 plan_build_kernel(void* plan, int cap, const void* ids, int T, const PlanAdapters ad) {
     const int N = ad.n_adapters;
+    pdl_launch_dependents();
+    pdl_wait_prior();
     __shared__ int smem[64];
     PlanView pv = plan_view(plan, cap, N);
     if (threadIdx.x == 0) {
@@ -210,6 +212,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1)
 plan_segments_kernel(void* plan, int cap, const int* seg_starts, const int* seg_adapter, int S, int T,
                      const PlanAdapters ad) {
     const int N = ad.n_adapters;
+    pdl_launch_dependents();
+    pdl_wait_prior();
     __shared__ int smem[64];
     PlanView pv = plan_view(plan, cap, N);
     const int tid = threadIdx.x;

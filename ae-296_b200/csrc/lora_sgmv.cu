@@ -156,6 +156,7 @@ __device__ __forceinline__ TileInfo tile_info(const SgmvParams& sp, const ApplyP
 template <typename T>
 __global__ void __launch_bounds__(kSgmvThreads, 1)
 sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ SgmvParams sp) {
+    pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* stage1 = smem;
@@ -170,6 +171,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const int D2_FULL = D1_FULL + 4, D2_EMPTY = D1_FULL + 6;
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
+    pdl_wait_prior();
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
