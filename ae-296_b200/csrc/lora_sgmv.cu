@@ -348,9 +348,19 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const bool live = row < t.valid;
             for (int nt = 0; nt < nnt; ++nt, ++nd) {
                 const int buf = nd & 1;
+                // the y slice of this row does not depend on the MMA: fetch all of it first, so
+                // sixteen loads are in flight while the accumulator is being produced
+                uint4 yv[kBN / 8];
+                const bool pre = live && !p.y_f32;
+                uint4* yrow = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)(t.row0 + row) * pj.ldy + nt * kBN);
+                if (pre) {
+#pragma unroll
+                    for (int q = 0; q < kBN / 8; ++q)
+                        if (nt * kBN + q * 8 < pj.h_out) yv[q] = yrow[q];
+                }
                 mbar_wait(bar(D2_FULL + buf), (nd >> 1) & 1, err, 20);
                 tc_fence_after();
-#pragma unroll 2
+#pragma unroll
                 for (int c = 0; c < kBN / 16; ++c) {
                     float v[16];
                     tc_ld16(tmem + lane_base + kD2Col + buf * kBN + c * 16, v);
@@ -361,24 +371,22 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                                                                    (long long)(t.row0 + row) * pj.ldy + col);
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
-                                float4 yv = yp[q];
-                                yv.x += t.scale * v[4 * q]; yv.y += t.scale * v[4 * q + 1];
-                                yv.z += t.scale * v[4 * q + 2]; yv.w += t.scale * v[4 * q + 3];
-                                yp[q] = yv;
+                                float4 y4 = yp[q];
+                                y4.x += t.scale * v[4 * q]; y4.y += t.scale * v[4 * q + 1];
+                                y4.z += t.scale * v[4 * q + 2]; y4.w += t.scale * v[4 * q + 3];
+                                yp[q] = y4;
                             }
                         } else {
-                            uint4* yp = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) +
-                                                                 (long long)(t.row0 + row) * pj.ldy + col);
 #pragma unroll
                             for (int q = 0; q < 2; ++q) {
-                                uint4 yv = yp[q];
+                                uint4 y4 = yv[2 * c + q];
                                 float f[8];
-                                Cvt<T>::unpack8(yv, f);
-                                yv.x = Cvt<T>::pack2(f[0] + t.scale * v[8 * q], f[1] + t.scale * v[8 * q + 1]);
-                                yv.y = Cvt<T>::pack2(f[2] + t.scale * v[8 * q + 2], f[3] + t.scale * v[8 * q + 3]);
-                                yv.z = Cvt<T>::pack2(f[4] + t.scale * v[8 * q + 4], f[5] + t.scale * v[8 * q + 5]);
-                                yv.w = Cvt<T>::pack2(f[6] + t.scale * v[8 * q + 6], f[7] + t.scale * v[8 * q + 7]);
-                                yp[q] = yv;
+                                Cvt<T>::unpack8(y4, f);
+                                y4.x = Cvt<T>::pack2(f[0] + t.scale * v[8 * q], f[1] + t.scale * v[8 * q + 1]);
+                                y4.y = Cvt<T>::pack2(f[2] + t.scale * v[8 * q + 2], f[3] + t.scale * v[8 * q + 3]);
+                                y4.z = Cvt<T>::pack2(f[4] + t.scale * v[8 * q + 4], f[5] + t.scale * v[8 * q + 5]);
+                                y4.w = Cvt<T>::pack2(f[6] + t.scale * v[8 * q + 6], f[7] + t.scale * v[8 * q + 7]);
+                                yrow[2 * c + q] = y4;
                             }
                         }
                     }
