@@ -127,6 +127,7 @@ __device__ __forceinline__ unsigned make_idesc(bool bf16, int M, int N) {
 
 struct TileInfo {
     int adapter, rank, row0, valid, cls;     // cls: 0 -> 16, 1 -> 32, 2 -> 64
+    int pos0;                                // sorted position of the tile's first row (index into v)
     float scale;
     long long a_row0;                        // first row of the A block in the [rows, h_in] view
     long long b_row0;                        // first row of the B block in the [rows, rank] view
@@ -141,6 +142,7 @@ __device__ __forceinline__ TileInfo tile_info(const SgmvParams& sp, const ApplyP
     t.adapter = pv.seg_adapter[seg];
     t.rank = pv.seg_rank[seg];
     t.row0 = pv.perm[b] + mt * kBM;
+    t.pos0 = b + mt * kBM;
     t.valid = min(kBM, (en - b) - mt * kBM);
     t.cls = t.rank == 16 ? 0 : t.rank == 32 ? 1 : 2;
     t.scale = p.scalings ? p.scalings[t.adapter] : p.scale;
@@ -180,6 +182,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const int n_tiles = (hdr.error || hdr.cap != p.cap) ? 0 : hdr.n_tiles;
     const int n_items = n_tiles * p.n_proj;
     const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
+    // tensor-parallel callers run the two halves separately and sum v in between
+    const bool do1 = !(p.flags & B200_LORA_ONLY_EXPAND), do2 = !(p.flags & B200_LORA_ONLY_SHRINK);
 
     if (tid == 0) {
         for (int s = 0; s < kS1; ++s) { mbar_init(bar(FULL1 + s), 1); mbar_init(bar(EMPTY1 + s), 1); }
@@ -209,7 +213,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const ProjArgs& pj = p.proj[proj];
             const int nkb = pj.h_in / kBK;
             const int n_abox = t.rank / 8;
-            for (int kb = 0; kb < nkb; ++kb, ++n1) {
+            for (int kb = 0; do1 && kb < nkb; ++kb, ++n1) {
                 const int s = n1 % kS1;
                 mbar_wait(bar(EMPTY1 + s), ((n1 / kS1) & 1) ^ 1, err, 11);
                 const unsigned dst = smem_u32(stage1 + s * kStage1);
@@ -223,7 +227,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                                   bar(FULL1 + s));
             }
             const int nnt = (pj.h_out + kBN - 1) / kBN;
-            for (int nt = 0; nt < nnt; ++nt, ++n2) {
+            for (int nt = 0; do2 && nt < nnt; ++nt, ++n2) {
                 const int s = n2 % kS2;
                 mbar_wait(bar(EMPTY2 + s), ((n2 / kS2) & 1) ^ 1, err, 12);
                 if (lane == 0) {
@@ -244,10 +248,10 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const ProjArgs& pj = p.proj[proj];
             const int nkb = pj.h_in / kBK;
             // phase 1: D1 = X . A^T     (D1 must have been drained by the epilogue of the previous item)
-            mbar_wait(bar(D1_EMPTY), (n_item & 1) ^ 1, err, 13);
+            if (do1) mbar_wait(bar(D1_EMPTY), (n_item & 1) ^ 1, err, 13);
             tc_fence_after();
             const unsigned idesc1 = make_idesc(bf16, kBM, t.rank);
-            for (int kb = 0; kb < nkb; ++kb, ++n1) {
+            for (int kb = 0; do1 && kb < nkb; ++kb, ++n1) {
                 const int s = n1 % kS1;
                 mbar_wait(bar(FULL1 + s), (n1 / kS1) & 1, err, 14);
                 tc_fence_after();
@@ -263,6 +267,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                 __syncwarp();
             }
             // phase 2: D2[buf] = V . B_slice^T
+            if (!do2) continue;
             mbar_wait(bar(V_READY), n_item & 1, err, 15);
             tc_fence_after();
             const unsigned layout = t.cls == 2 ? 2u : t.cls == 1 ? 4u : 6u;
@@ -303,20 +308,39 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes
-            mbar_wait(bar(D1_FULL), n_item & 1, err, 18);
-            tc_fence_after();
             float d1[64];
+            float* vrow = ws.v + ((size_t)proj * p.cap + t.pos0 + row) * kMaxRank;
+            if (do1) {
+                mbar_wait(bar(D1_FULL), n_item & 1, err, 18);
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (c * 16 < t.rank) {
-                    float v[16];
-                    tc_ld16(tmem + lane_base + kD1Col + c * 16, v);
+                for (int c = 0; c < 4; ++c) {
+                    if (c * 16 < t.rank) {
+                        float v[16];
+                        tc_ld16(tmem + lane_base + kD1Col + c * 16, v);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) d1[c * 16 + i] = v[i];
+                        for (int i = 0; i < 16; ++i) d1[c * 16 + i] = v[i];
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(bar(D1_EMPTY));
+                if (!do2) {                                  // shrink half only: publish the fp32 rows
+                    if (row < t.valid) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (c * 4 < t.rank)
+                                reinterpret_cast<float4*>(vrow)[c] = make_float4(d1[4 * c], d1[4 * c + 1], d1[4 * c + 2], d1[4 * c + 3]);
+                    }
+                    continue;
+                }
+            } else {                                         // expand half only: v was summed by the caller
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (c * 4 < t.rank && row < t.valid) f = reinterpret_cast<const float4*>(vrow)[c];
+                    d1[4 * c] = f.x; d1[4 * c + 1] = f.y; d1[4 * c + 2] = f.z; d1[4 * c + 3] = f.w;
                 }
             }
-            tc_fence_before();
-            mbar_arrive(bar(D1_EMPTY));
             mbar_wait(bar(V_FREE), (n_item & 1) ^ 1, err, 19);       // previous item's phase 2 finished with V
             {
                 const int rb = t.rank * 2;                            // row bytes: 32, 64, 128

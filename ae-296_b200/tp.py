@@ -47,8 +47,10 @@ class TPLora:
         self.batch = LoraBatch(max_tokens, n_adapters, h_in_shard, n_proj, device)
         self._v = self.batch.workspace.v_view()
 
-    def set_ids(self, ids: torch.Tensor, pool_shard: AdapterPool) -> "TPLora":
-        self.batch.set_ids(ids, pool_shard, tiles=False)     # both halves must stay separable
+    def set_ids(self, ids: torch.Tensor, pool_shard: AdapterPool, tiles: bool = False) -> "TPLora":
+        """``tiles=True`` sends tall contiguous runs (prompts) to the tcgen05 tile kernel, which
+        then runs as two halves too (shrink half publishes v, expand half reads the summed v)."""
+        self.batch.set_ids(ids, pool_shard, tiles=tiles)
         return self
 
     def apply(self, projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], layer: int) -> None:

@@ -142,7 +142,7 @@ def tensor_parallel_arm(args, wl, rank, local, world, dev):
     stream = torch.cuda.Stream(dev)
 
     def one_pass():
-        eng.set_ids(ids, pools["q"])
+        eng.set_ids(ids, pools["q"], tiles=wl.seq_lens is not None)
         for l in range(n_layers):
             eng.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
             eng.apply([(x_o[l], ys["o"][l], pools["o"])], l)
