@@ -65,7 +65,7 @@ struct PlanView {
     int* ws_adapter;    // [cap]
     int* ws_rank;       // [cap]
     int* unit_tab;      // [16 * cap][16]  one record per weight unit (see UnitRec)
-    int* tile_tab;      // [cap]       (seg << 12) | m-tile, for tall segments (cap/kTallMin used)
+    int* tile_tab;      // [cap]       two words per tile of a tall run: first sorted position, (seg << 8) | (rows - 1)
     int* hist;          // [n_adapters + 1]
 };
 

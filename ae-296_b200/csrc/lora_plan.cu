@@ -4,7 +4,7 @@
 //   perm         stable counting sort (token order kept inside one adapter)
 //   seg_*        one segment per adapter that has tokens, ascending adapter id
 //   unit_tab     the <= 16 KB weight units the BGMV kernels walk: short segments first
-//   tile_tab     128-row tiles of tall contiguous segments for the tensor-core kernel
+//   tile_tab     128-row tiles of tall runs (>= 32 consecutive rows of one adapter) for the tensor-core kernel
 // It replaces the reference's precomputed index tensor (lightllm/models/lora_gpu.py:120,124)
 // and is integer work only: the tests require it bit-exact against a stable argsort.
 #include "lora_common.cuh"
@@ -110,7 +110,28 @@ __device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* 
     __syncthreads();
 }
 
-// Phase B: classify segments, cut them into work segments, lay out units and tiles.
+// Walks one adapter segment (sorted positions [b, e)) as a sequence of pieces: maximal runs of
+// consecutive token rows that are long enough for the tensor-core tiles ("tall", kind 1), and the
+// stretches of positions in between (kind 0).  f(kind, begin, end).
+template <class F>
+__device__ __forceinline__ void walk_segment(const int* perm, int b, int e, bool identity, bool tile_rank, F f) {
+    int i = b, short_begin = b;
+    while (i < e) {
+        int j = i + 1;
+        if (identity) j = e;
+        else while (j < e && perm[j] == perm[j - 1] + 1) ++j;
+        if (tile_rank && j - i >= kTallMin) {
+            if (i > short_begin) f(0, short_begin, i);
+            f(1, i, j);
+            short_begin = j;
+        }
+        i = j;
+    }
+    if (e > short_begin) f(0, short_begin, e);
+}
+
+// Phase B: split segments into tall runs and short stretches, cut both into work segments of at
+// most kChunkTok tokens, lay out unit records (short ones first) and the tile list.
 __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
     const int* ranks = ad.ranks;
     const long long* cum_ranks = ad.cum_ranks;
@@ -119,13 +140,14 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
     int* warp_sums = smem;
     const int S = pv.hdr->n_segs;
     const bool identity = pv.hdr->identity != 0;
-    // pass 0 totals the units of short segments (they are listed first); pass 1 writes
+    // pass 0 totals the units of short stretches (they are listed first); pass 1 writes
     int tot_short = 0, tot_tall = 0, tot_tiles = 0, tot_ws = 0;
     for (int pass = 0; pass < 2; ++pass) {
         int c_short = 0, c_tall = 0, c_tiles = 0, c_ws = 0;
         for (int base = 0; base < S; base += kPlanThreads) {
             int s = base + tid;
-            int us = 0, ut = 0, nt = 0, r = 0, tall = 0, len = 0, nchunk = 0, b = 0, a = 0;
+            int us = 0, ut = 0, nt = 0, r = 0, nchunk = 0, b = 0, e = 0, a = 0, nsub = 0;
+            bool tile_rank = false;
             if (s < S) {
                 a = pv.seg_adapter[s];
                 r = ranks ? ranks[a] : r_pool;
@@ -134,17 +156,16 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
                 if (r < 1) r = 1;
                 if (r > kMaxRank) r = kMaxRank;
                 b = pv.seg_start[s];
-                int e = pv.seg_start[s + 1];
-                len = e - b;
-                bool contig = identity || (pv.perm[e - 1] - pv.perm[b] == len - 1);
+                e = pv.seg_start[s + 1];
+                nsub = n_sub(pad_rank(r));
                 // tensor-core tiles take ranks 16/32/64 in a layout whose B rows are contiguous
-                const bool tile_rank = (r == 16 || r == 32 || r == 64) && (cum_ranks || r == r_pool);
-                tall = (len >= kTallMin && contig && tile_rank) ? 1 : 0;
-                nchunk = (len + kChunkTok - 1) / kChunkTok;
-                int u = nchunk * n_sub(pad_rank(r));
-                us = tall ? 0 : u;
-                ut = tall ? u : 0;
-                nt = tall ? (len + kTileM - 1) / kTileM : 0;
+                tile_rank = (r == 16 || r == 32 || r == 64) && (cum_ranks || r == r_pool);
+                walk_segment(pv.perm, b, e, identity, tile_rank, [&](int kind, int pb, int pe) {
+                    const int ch = (pe - pb + kChunkTok - 1) / kChunkTok;
+                    nchunk += ch;
+                    if (kind) { ut += ch * nsub; nt += (pe - pb + kTileM - 1) / kTileM; }
+                    else us += ch * nsub;
+                });
             }
             int t0, t1, t2, t3;
             int o_s = block_scan_excl(us, t0, warp_sums);
@@ -153,28 +174,41 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
             int o_w = block_scan_excl(nchunk, t3, warp_sums);
             if (pass == 1 && s < S) {
                 pv.seg_rank[s] = r;
-                pv.seg_flags[s] = tall;
-                int u0 = tall ? tot_short + c_tall + o_t : c_short + o_s;
-                const int w0 = c_ws + o_w;
-                const int per = (len + nchunk - 1) / nchunk;         // balanced chunk length
-                const int nsub = n_sub(pad_rank(r));
+                pv.seg_flags[s] = nt > 0 ? 1 : 0;
+                int u_short = c_short + o_s, u_tall = tot_short + c_tall + o_t;
+                int w = c_ws + o_w, tile = c_tiles + o_m;
                 const long long cum = cum_ranks ? cum_ranks[a] : 0;
-                for (int c = 0; c < nchunk; ++c) {
-                    const int cb = b + min(c * per, len), ce = b + min((c + 1) * per, len);
-                    pv.ws_start[w0 + c] = cb;
-                    pv.ws_adapter[w0 + c] = a;
-                    pv.ws_rank[w0 + c] = r;
-                    UnitRec rec;
-                    rec.adapter = a; rec.rank = r; rec.ntok = (short)(ce - cb); rec.wseg = w0 + c; rec.start = cb;
-                    rec.scale = ad.scalings ? ad.scalings[a] : ad.scale;
-                    rec.cum_lo = (int)(cum & 0xffffffffll); rec.cum_hi = (int)(cum >> 32);
-                    for (int i = 0; i < 8; ++i) rec.tok[i] = pv.perm[cb + min(i, ce - cb - 1)];
-                    for (int j = 0; j < nsub; ++j) {
-                        rec.sub = (short)j;
-                        reinterpret_cast<UnitRec*>(pv.unit_tab)[u0 + c * nsub + j] = rec;
+                const float scale = ad.scalings ? ad.scalings[a] : ad.scale;
+                walk_segment(pv.perm, b, e, identity, tile_rank, [&](int kind, int pb, int pe) {
+                    const int len = pe - pb;
+                    const int ch = (len + kChunkTok - 1) / kChunkTok;
+                    const int per = (len + ch - 1) / ch;             // balanced chunk length
+                    int& u = kind ? u_tall : u_short;
+                    for (int c = 0; c < ch; ++c) {
+                        const int cb = pb + min(c * per, len), ce = pb + min((c + 1) * per, len);
+                        pv.ws_start[w] = cb;
+                        pv.ws_adapter[w] = a;
+                        pv.ws_rank[w] = r;
+                        UnitRec rec;
+                        rec.adapter = a; rec.rank = r; rec.ntok = (short)(ce - cb); rec.wseg = w; rec.start = cb;
+                        rec.scale = scale;
+                        rec.cum_lo = (int)(cum & 0xffffffffll); rec.cum_hi = (int)(cum >> 32);
+                        for (int i = 0; i < 8; ++i) rec.tok[i] = pv.perm[cb + min(i, ce - cb - 1)];
+                        for (int j = 0; j < nsub; ++j) {
+                            rec.sub = (short)j;
+                            reinterpret_cast<UnitRec*>(pv.unit_tab)[u + j] = rec;
+                        }
+                        u += nsub;
+                        ++w;
                     }
-                }
-                for (int m = 0; m < nt; ++m) pv.tile_tab[c_tiles + o_m + m] = (s << 12) | m;
+                    if (kind) {
+                        for (int m = 0; m * kTileM < len; ++m) {
+                            pv.tile_tab[2 * tile] = pb + m * kTileM;
+                            pv.tile_tab[2 * tile + 1] = (s << 8) | (min(kTileM, len - m * kTileM) - 1);
+                            ++tile;
+                        }
+                    }
+                });
             }
             c_short += t0; c_tall += t1; c_tiles += t2; c_ws += t3;
         }

@@ -1,7 +1,7 @@
 // Prefill SGMV for tall segments: TMA-fed tcgen05 tiles with TMEM accumulators.
 //
-// A "tall" segment is a run of >= 32 consecutive token rows that share one adapter of rank 16,
-// 32 or 64 (the plan marks them); everything else stays on the BGMV kernels.  One work item is
+// A "tall" run is >= 32 consecutive token rows that share one adapter of rank 16, 32 or 64
+// (the plan finds them inside the adapter segments); everything else stays on the BGMV kernels.  One work item is
 // (128-row tile of a tall segment, projection).  For it a CTA computes, entirely on chip,
 //
 //   phase 1   D1[128, r]    = X[128, h_in] . A^T          tcgen05.mma, M=128 N=r, K in blocks of 64
@@ -136,14 +136,13 @@ struct TileInfo {
 __device__ __forceinline__ TileInfo tile_info(const SgmvParams& sp, const ApplyParams& p, const PlanView& pv,
                                               int tile, int proj) {
     TileInfo t;
-    const int e = pv.tile_tab[tile];
-    const int seg = e >> 12, mt = e & 0xfff;
-    const int b = pv.seg_start[seg], en = pv.seg_start[seg + 1];
+    const int pos0 = pv.tile_tab[2 * tile], e1 = pv.tile_tab[2 * tile + 1];
+    const int seg = e1 >> 8;
     t.adapter = pv.seg_adapter[seg];
     t.rank = pv.seg_rank[seg];
-    t.row0 = pv.perm[b] + mt * kBM;
-    t.pos0 = b + mt * kBM;
-    t.valid = min(kBM, (en - b) - mt * kBM);
+    t.pos0 = pos0;
+    t.row0 = pv.perm[pos0];                   // rows of a run are consecutive
+    t.valid = (e1 & 255) + 1;
     t.cls = t.rank == 16 ? 0 : t.rank == 32 ? 1 : 2;
     t.scale = p.scalings ? p.scalings[t.adapter] : p.scale;
     t.a_row0 = block_row0(p, t.adapter, t.rank);
@@ -180,7 +179,15 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     unsigned* err = &ws.ctl->error;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_tiles = (hdr.error || hdr.cap != p.cap) ? 0 : hdr.n_tiles;
-    const int n_items = n_tiles * p.n_proj;
+    // fewer tiles than SMs: cut each tile's output columns into `nsplit` parts handled by different
+    // CTAs (each redoes the cheap phase 1 from L2), aiming at >= 2 items per CTA
+    const int base_items = n_tiles * p.n_proj;
+    int nsplit = 1;
+    if (base_items > 0 && base_items < (int)gridDim.x && !(p.flags & B200_LORA_ONLY_SHRINK))
+        nsplit = min(8, max(1, (2 * (int)gridDim.x + base_items - 1) / base_items));
+    for (int i = 0; i < p.n_proj; ++i)                    // every part must own at least one column slice
+        nsplit = min(nsplit, (p.proj[i].h_out + kBN - 1) / kBN);
+    const int n_items = base_items * nsplit;
     const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
     // tensor-parallel callers run the two halves separately and sum v in between
     const bool do1 = !(p.flags & B200_LORA_ONLY_EXPAND), do2 = !(p.flags & B200_LORA_ONLY_SHRINK);
@@ -208,7 +215,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         // ================= TMA producer =================
         unsigned n1 = 0, n2 = 0;        // ring uses so far
         for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int proj = item / n_tiles, tile = item - proj * n_tiles;
+            const int part = item % nsplit, rest = item / nsplit;
+            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             const int nkb = pj.h_in / kBK;
@@ -226,8 +234,9 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                     tensor_g2s_2d(dst + kXTile + lane * 1024, &sp.amap[proj], kb * kBK, (int)t.a_row0 + lane * 8,
                                   bar(FULL1 + s));
             }
-            const int nnt = (pj.h_out + kBN - 1) / kBN;
-            for (int nt = 0; do2 && nt < nnt; ++nt, ++n2) {
+            const int nnt_all = (pj.h_out + kBN - 1) / kBN;
+            const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
+            for (int nt = nt0; do2 && nt < nnt; ++nt, ++n2) {
                 const int s = n2 % kS2;
                 mbar_wait(bar(EMPTY2 + s), ((n2 / kS2) & 1) ^ 1, err, 12);
                 if (lane == 0) {
@@ -243,7 +252,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         unsigned n1 = 0, n2 = 0, nd = 0, n_item = 0;
         const bool bf16 = Cvt<T>::is_bf16;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
-            const int proj = item / n_tiles, tile = item - proj * n_tiles;
+            const int part = item % nsplit, rest = item / nsplit;
+            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             const int nkb = pj.h_in / kBK;
@@ -273,8 +283,9 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const unsigned layout = t.cls == 2 ? 2u : t.cls == 1 ? 4u : 6u;
             const unsigned sbo = 8u * t.rank * 2u;
             const unsigned idesc2 = make_idesc(bf16, kBM, kBN);
-            const int nnt = (pj.h_out + kBN - 1) / kBN;
-            for (int nt = 0; nt < nnt; ++nt, ++n2, ++nd) {
+            const int nnt_all = (pj.h_out + kBN - 1) / kBN;
+            const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
+            for (int nt = nt0; nt < nnt; ++nt, ++n2, ++nd) {
                 const int s = n2 % kS2, buf = nd & 1;
                 mbar_wait(bar(FULL2 + s), (n2 / kS2) & 1, err, 16);
                 mbar_wait(bar(D2_EMPTY + buf), ((nd >> 1) & 1) ^ 1, err, 17);
@@ -304,7 +315,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         const unsigned lane_base = (unsigned)(quad * 32) << 16;
         unsigned nd = 0, n_item = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
-            const int proj = item / n_tiles, tile = item - proj * n_tiles;
+            const int part = item % nsplit, rest = item / nsplit;
+            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes
@@ -368,9 +380,10 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> tensor-core reads
             mbar_arrive(bar(V_READY));
             // ---- D2 slices -> y
-            const int nnt = (pj.h_out + kBN - 1) / kBN;
+            const int nnt_all = (pj.h_out + kBN - 1) / kBN;
+            const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
             const bool live = row < t.valid;
-            for (int nt = 0; nt < nnt; ++nt, ++nd) {
+            for (int nt = nt0; nt < nnt; ++nt, ++nd) {
                 const int buf = nd & 1;
                 // the y slice of this row does not depend on the MMA: fetch all of it first, so
                 // sixteen loads are in flight while the accumulator is being produced
