@@ -367,7 +367,7 @@ int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, cons
     // (tickets, arrival counters, slot masks, error word) to start at zero: clear that prefix
     // of the workspace part; the plan part is rebuilt from scratch by every call.
     const size_t pb = (b200_lora_plan_bytes(n_tokens, n_adapters) + 255) & ~size_t(255);
-    const size_t ctl_bytes = sizeof(WorkspaceCtl) + 4 * ((ws_counter_words(n_tokens) + 3) & ~size_t(3)) +
+    const size_t ctl_bytes = sizeof(WorkspaceCtl) + 8 * ((ws_counter_words(n_tokens) + 3) & ~size_t(3)) +
                              8 * ws_counter_words(n_tokens);
     e = cudaMemsetAsync(static_cast<char*>(scratch) + pb, 0, ctl_bytes, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e);

@@ -279,7 +279,8 @@ struct Run {
 // completed the (projection, work segment).
 template <typename T>
 __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const WorkspaceView& ws, const Run& run,
-                                             float (&acc)[4][4], float* red, int* s_flag, int tid) {
+                                             float (&acc)[4][4], float* red, int* s_flag, int tid,
+                                             unsigned ready_val = 0u) {
     const int lane = tid & 31, warp = tid >> 5;
     const int r = run.rank, rp = r + 4;
     const int MB = r >= 16 ? r / 16 : 1;
@@ -315,8 +316,14 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         else ws.partial[(size_t)run.first_kc * cstride + o] = s;
     }
     cons_sync();                                           // partial written by all threads, red free again
-    if (whole) return;                                     // nothing to combine across CTAs
     const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
+    if (whole) {                                           // nothing to combine across CTAs
+        if (ready_val && tid == 0) {
+            __threadfence();
+            *reinterpret_cast<volatile unsigned*>(&ws.ready[cidx]) = ready_val;
+        }
+        return;
+    }
     if (tid == 0) {
         atomicOr(&ws.masks[cidx], 1ull << run.first_kc);
         const unsigned old = atom_add_acq_rel(&ws.counters[cidx], (unsigned)run.count);
@@ -349,6 +356,10 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         if (tid == 0) { ws.counters[cidx] = 0u; ws.masks[cidx] = 0ull; }
     }
     cons_sync();                                           // s_flag may be rewritten by the next flush
+    if (ready_val && *s_flag && tid == 0) {                // v is final: let the expand units go
+        __threadfence();
+        *reinterpret_cast<volatile unsigned*>(&ws.ready[cidx]) = ready_val;
+    }
 }
 
 template <typename T>
@@ -701,6 +712,179 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
     TRACE_FLUSH(tid == 0, 5)
 }
 
+// =============================================================================================
+// fused shrink -> expand
+// =============================================================================================
+// One launch per apply: every CTA first streams its range of shrink units, then a marker that
+// makes its consumers publish whatever run they still hold, then its range of expand units.
+// Before loading an expand unit the producer waits (bounded) until the unit's (projection, work
+// segment) has been marked ready by whichever CTA finished its v; ready words hold the launch
+// epoch + 1, so they never need clearing.  Shrink work never waits on anything, so the CTAs
+// make progress in any order as long as the grid is resident (it is sized to 2 CTAs per SM).
+constexpr int kFusedStage = kShrinkStage > kExpandStage ? kShrinkStage : kExpandStage;
+constexpr int kFusedSmem = kStages * kFusedStage + kRedBytes + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
+static_assert(kCtasPerSm * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
+enum { kKindShrink = 0, kKindExpand = 1, kKindFlush = 2 };
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(const __grid_constant__ ApplyParams p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    float* red = reinterpret_cast<float*>(smem + kStages * kFusedStage);
+    Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kFusedStage + kRedBytes);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
+    int* s_flag = reinterpret_cast<int*>(bars + 2 * kStages);
+
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[kStages + s]), kConsWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait_prior();
+
+    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
+    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
+    const PlanHeader hdr = *pv.hdr;
+    const bool dead = hdr.error || hdr.cap != p.cap;
+    const int n_units = dead ? 0 : ((p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short);
+    const int n_a = n_units * p.total_super_in, n_b = n_units * p.total_super_out;
+    const int per_a = (n_a + (int)gridDim.x - 1) / (int)gridDim.x, per_b = (n_b + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int first_a = blockIdx.x * per_a, first_b = blockIdx.x * per_b;
+    const int nl_a = max(0, min(per_a, n_a - first_a)), nl_b = max(0, min(per_b, n_b - first_b));
+    const int n_total = nl_a + 1 + nl_b;                   // shrink units, flush marker, expand units
+    unsigned* err = &ws.ctl->error;
+    const unsigned ready_val = *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) + 1u;
+
+    if (warp >= kConsWarps) {
+        // ---------------- producer warps (alternate items) ----------------
+        const int pw = warp - kConsWarps;
+        Cursor cur;
+        cur.unit = cur.sp = cur.proj = cur.super = 0;
+        int rec = 0;
+        bool have_a = false, have_b = false;
+        for (int n = pw; n < n_total; n += kProdWarps) {
+            const int s = n % kStages;
+            const unsigned ph = (n / kStages) & 1;
+            Meta* slot = &meta[n % kMetaSlots];
+            const unsigned full = smem_u32(&bars[s]);
+            if (n == nl_a) {                                   // flush marker
+                mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 5);
+                if (lane == 0) { slot->valid = 0; slot->pad[0] = kKindFlush; }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full);
+                continue;
+            }
+            const bool expand = n > nl_a;
+            if (!expand && !have_a) { cur = cursor_at(p, first_a + n, n_units, false); have_a = true; rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0; }
+            if (expand && !have_b) { cur = cursor_at(p, first_b + (n - nl_a - 1), n_units, true); have_b = true; rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0; }
+            const Item it = make_item(p, rec, cur, expand);
+            mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, expand ? 3 : 1);
+            publish_meta(slot, rec, it, lane);
+            if (lane == 0) slot->pad[0] = expand ? kKindExpand : kKindShrink;
+            __syncwarp();
+            const unsigned stage = smem_u32(smem + s * kFusedStage);
+            if (!it.valid) {
+                if (lane == 0) mbar_arrive(full);
+            } else if (!expand) {
+                shrink_produce<T>(p, it, rec, stage, full, lane);
+            } else {
+                const int wseg = __shfl_sync(0xffffffffu, rec, 4);
+                if (lane == 0) {                               // v of this (projection, work segment) final?
+                    const volatile unsigned* flag = &ws.ready[(size_t)it.proj * p.cap + wseg];
+                    unsigned i = 0;
+                    while (*flag != ready_val) {
+                        if (++i >= kSpinLimit || ((i & 0x3fffu) == 0 && *reinterpret_cast<volatile unsigned*>(err) != 0u)) {
+                            atomicMax(err, 6u);
+                            break;
+                        }
+                    }
+                    __threadfence();
+                    asm volatile("fence.proxy.async;" ::: "memory");   // generic writes of v -> bulk-copy reads
+                }
+                __syncwarp();
+                expand_produce<T>(p, ws, it, rec, stage, full, lane);
+            }
+            // advance this warp's cursor by kProdWarps items and fetch the next record
+            Cursor nxt = cur;
+#pragma unroll
+            for (int q = 0; q < kProdWarps; ++q) cursor_next(p, n_units, expand, nxt);
+            const int n2 = n + kProdWarps;
+            const bool same_phase = expand ? (n2 < n_total) : (n2 < nl_a);
+            cur = nxt;
+            rec = (same_phase && lane < 16) ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
+        }
+    } else {
+        // ---------------- consumer warps ----------------
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        Run run;
+        run.proj = -1; run.wseg = -1; run.count = 0;
+        run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
+        for (int n = 0; n < n_total; ++n) {
+            const int s = n % kStages;
+            const unsigned ph = (n / kStages) & 1;
+            mbar_wait(smem_u32(&bars[s]), ph, err, 2);
+            const Meta& m = meta[n % kMetaSlots];
+            const int kind = m.pad[0];
+            unsigned char* stage = smem + s * kFusedStage;
+            if (kind == kKindFlush) {
+                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, ready_val);
+                run.count = 0; run.proj = -1; run.wseg = -1;
+            } else if (kind == kKindShrink) {
+                if (m.valid) {
+                    if (m.proj != run.proj || m.u.wseg != run.wseg) {
+                        if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, ready_val);
+                        run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
+                        run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
+                    }
+                    shrink_consume<T>(m, stage, acc, tid);
+                    ++run.count;
+                }
+            } else {
+                if (m.valid) {
+                    switch (m.u.rank) {
+                        case 8:  expand_consume<T, 8>(p, m, stage, tid); break;
+                        case 16: expand_consume<T, 16>(p, m, stage, tid); break;
+                        case 32: expand_consume<T, 32>(p, m, stage, tid); break;
+                        default: expand_consume<T, 64>(p, m, stage, tid); break;
+                    }
+                }
+                cons_sync();
+                if (m.valid && !p.y_f32) {
+                    const ProjArgs& pj = p.proj[m.proj];
+                    const int jc = kSuper / n_sub(m.u.rank);
+                    const int cpt = jc / 8, cpt_shift = 31 - __clz(cpt);
+                    const int c = tid & (cpt - 1), rstep = kConsThreads >> cpt_shift;
+                    if (c * 8 < m.width_ok) {
+                        for (int row = tid >> cpt_shift; row < m.u.ntok; row += rstep) {
+                            const uint4 val = *reinterpret_cast<const uint4*>(stage + kWTile + row * (jc * 2 + kYPad) + c * 16);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + c * 8) = val;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {                                            // the last CTA out advances the epoch
+        __threadfence();
+        const unsigned d = atomicAdd(&ws.ctl->done[0], 1u);
+        if (d == gridDim.x - 1) {
+            ws.ctl->done[0] = 0u;
+            *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) = ready_val;
+        }
+    }
+}
+
 constexpr int kShrinkSmem = kStages * kShrinkStage + kRedBytes + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
 constexpr int kExpandSmem = kStages * kExpandStage + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
 static_assert(kCtasPerSm * (kShrinkSmem + 1024) <= 233472 && kCtasPerSm * (kExpandSmem + 1024) <= 233472,
@@ -716,9 +900,13 @@ cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(bgmv_expand_tma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpandSmem);
         if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(bgmv_fused_tma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmem);
+        if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int grid = n_sm * kCtasPerSm;
+    if (!(p.flags & (B200_LORA_ONLY_EXPAND | B200_LORA_ONLY_SHRINK | B200_LORA_TWO_KERNELS)))
+        return launch_pdl(bgmv_fused_tma_kernel<T>, grid, kThreads, kFusedSmem, s, p);
     cudaError_t e = cudaSuccess;
     if (!(p.flags & B200_LORA_ONLY_EXPAND)) e = launch_pdl(bgmv_shrink_tma_kernel<T>, grid, kThreads, kShrinkSmem, s, p);
     if (e == cudaSuccess && !(p.flags & B200_LORA_ONLY_SHRINK))
