@@ -5,7 +5,7 @@
 Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM (CUDA-graph
 replay of the whole pass, CUDA-event timed, max over ranks); `e2e` is the same pass driven
 from pinned host buffers through the public ops, host<->device copies inside the timed
-region; `roofline` is the expand kernel (the larger half of the traffic) timed alone;
+region; `roofline` is the fused shrink->expand kernel (the pass without the plan kernel);
 `cpu_baseline` is the reference's CPU LoRA arithmetic timed on this host's cores.
 With N > 1 each rank holds its own adapters and batch (placement by adapter, no collective).
 """
@@ -50,7 +50,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -256,7 +256,7 @@ def main():
             batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l, flags)
             batch.apply([(x_o[l], ys["o"][l], pools["o"])], l, flags)
 
-    launches_per_pass = 1 + n_layers * (6 if use_tiles else 4)
+    launches_per_pass = 1 + n_layers * (4 if use_tiles else 2)
 
     def capture(flags=0, plan=True):
         g = torch.cuda.CUDAGraph()
@@ -313,26 +313,30 @@ def main():
     e = 2
     exp_bytes = sum(rsum * p.h_out * e + 2 * T * p.h_out * e for p in wl.projections) * n_layers
     shr_bytes = sum(rsum * p.h_in * e + T * p.h_in * e + 4 * T for p in wl.projections) * n_layers
+    # dominant kernel: the fused shrink->expand BGMV kernel (one launch per apply); timed as the whole
+    # pass without the plan kernel.  The two halves are also timed alone (separate kernels).
+    ms_noplan = timed(capture(0, plan=False), args.steps, 3)
     ms_exp = timed(capture(_lib.ONLY_EXPAND, plan=False), args.steps, 3)
     ms_shr = timed(capture(_lib.ONLY_SHRINK, plan=False), args.steps, 3)
     us_plan = timed(capture_plan_only(), args.steps, 3) * 1e3 / 8
-    n_exp_launch = n_layers * 2
-    # DRAM bytes per expand launch from the ncu capture summarised in
-    # profiles/bgmv_tma_cfg1_ncu_full.md (dram__bytes_read.sum + dram__bytes_write.sum, mean of the
-    # q/k/v and the o launch of one layer; one launch = one layer at any depth)
-    traffic = 42.25e6 if wl.cfg == 1 else None
-    ach = exp_bytes / (ms_exp * 1e-3) / 1e9
+    n_launch = n_layers * 2
+    pass_bytes = wl.bytes_per_layer() * n_layers
+    # DRAM bytes per launch from the ncu capture summarised in profiles/bgmv_fused_cfg1_ncu.md
+    # (dram__bytes_read.sum + dram__bytes_write.sum, mean of the q/k/v and the o launch of one layer)
+    traffic = 83.1e6 if (wl.cfg == 1 and not use_tiles) else None
+    ach = pass_bytes / (ms_noplan * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "bgmv_expand_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
-        "frac": ach / peak, "traffic": traffic, "peak_source": peak_src,
-        "bytes_per_launch": exp_bytes / n_exp_launch, "us_per_launch": ms_exp * 1e3 / n_exp_launch,
-        "frac_of_8TBs_nominal": ach / 8000.0,
-        "shrink": {"kernel": "bgmv_shrink_kernel", "achieved": shr_bytes / (ms_shr * 1e-3) / 1e9,
-                   "frac": shr_bytes / (ms_shr * 1e-3) / 1e9 / peak, "us_per_launch": ms_shr * 1e3 / n_exp_launch},
+        "bound": "hbm", "kernel": "bgmv_fused_tma_kernel" if not use_tiles else "sgmv_tile_kernel + bgmv_fused_tma_kernel",
+        "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
+        "peak_source": peak_src, "bytes_per_launch": pass_bytes / n_launch,
+        "us_per_launch": ms_noplan * 1e3 / n_launch, "frac_of_8TBs_nominal": ach / 8000.0,
+        "expand_half": {"achieved": exp_bytes / (ms_exp * 1e-3) / 1e9, "frac": exp_bytes / (ms_exp * 1e-3) / 1e9 / peak,
+                        "us_per_launch": ms_exp * 1e3 / n_launch},
+        "shrink_half": {"achieved": shr_bytes / (ms_shr * 1e-3) / 1e9, "frac": shr_bytes / (ms_shr * 1e-3) / 1e9 / peak,
+                        "us_per_launch": ms_shr * 1e3 / n_launch},
         "plan_us": us_plan,
-        "whole_pass": {"bytes": wl.bytes_per_layer() * n_layers,
-                       "achieved": wl.bytes_per_layer() * n_layers / (ms * 1e-3) / 1e9,
-                       "frac": wl.bytes_per_layer() * n_layers / (ms * 1e-3) / 1e9 / peak},
+        "whole_pass": {"bytes": pass_bytes, "achieved": pass_bytes / (ms * 1e-3) / 1e9,
+                       "frac": pass_bytes / (ms * 1e-3) / 1e9 / peak},
     }
 
     # end to end from pinned host buffers through the public ops
