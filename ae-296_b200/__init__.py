@@ -6,7 +6,7 @@ interface of the reference's LoRA layer objects.
 """
 from . import workloads                                      # noqa: F401
 from .pool import AdapterPool, MAX_RANK                      # noqa: F401
-from ._lib import LoraError, MID_ROUND, NO_TENSOR            # noqa: F401
+from ._lib import LoraError, MID_ROUND, NO_TENSOR, DELTA_THEN_ADD   # noqa: F401
 from .ops import (LoraBatch, LoraPlan, LoraWorkspace, add_lora_bgmv, add_lora_bgmv_static,   # noqa: F401
                   add_lora_bgmv_v2, add_lora_sgmv, adapters_of, apply)
 from . import ops                                            # noqa: F401

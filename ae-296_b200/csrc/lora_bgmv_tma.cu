@@ -472,7 +472,7 @@ __device__ __forceinline__ void expand_produce(const ApplyParams& p, const Works
     const int r = m.rank;
     const int jc = kSuper / n_sub(r);
     const unsigned w_bytes = m.width_ok * r * 2;
-    const unsigned y_bytes = p.y_f32 ? 0u : m.width_ok * 2;
+    const unsigned y_bytes = (p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD)) ? 0u : m.width_ok * 2;
     const unsigned v_bytes = r * 4;
     if (lane == 0) mbar_arrive_expect_tx(bar, w_bytes + m.ntok * (y_bytes + v_bytes));
     __syncwarp();
@@ -597,6 +597,13 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
                 float2 yv = *yp;
                 yv.x += d0; yv.y += d1;
                 *yp = yv;
+            } else if (p.flags & B200_LORA_DELTA_THEN_ADD) {
+                // the delta is rounded to the I/O type and added to y in that type, two outputs
+                // per reduction, straight in global memory: no y tile, no write-back
+                T* yp = reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[g] * pj.ldy + m.c0 + j;
+                const unsigned d = Cvt<T>::pack2(d0, d1);
+                if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
+                else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
             } else {
                 unsigned* yp = reinterpret_cast<unsigned*>(ysb + g * ypitch + j * 2);
                 const unsigned w = *yp;
@@ -691,8 +698,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             }
         }
         TRACE_MARK(4)
-        cons_sync();
-        if (m.valid && !p.y_f32) {
+        const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
+        if (staged) cons_sync();
+        if (m.valid && staged) {
             // coalesced write-back of the updated y tile, 16 bytes per thread
             const ProjArgs& pj = p.proj[m.proj];
             const int jc = kSuper / n_sub(m.u.rank);
@@ -856,8 +864,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                         default: expand_consume<T, 64>(p, m, stage, tid); break;
                     }
                 }
-                cons_sync();
-                if (m.valid && !p.y_f32) {
+                const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
+                if (staged) cons_sync();
+                if (m.valid && staged) {
                     const ProjArgs& pj = p.proj[m.proj];
                     const int jc = kSuper / n_sub(m.u.rank);
                     const int cpt = jc / 8, cpt_shift = 31 - __clz(cpt);

@@ -319,6 +319,7 @@ def main():
     ms_exp = timed(capture(_lib.ONLY_EXPAND, plan=False), args.steps, 3)
     ms_shr = timed(capture(_lib.ONLY_SHRINK, plan=False), args.steps, 3)
     us_plan = timed(capture_plan_only(), args.steps, 3) * 1e3 / 8
+    ms_dta = timed(capture(_lib.DELTA_THEN_ADD, plan=False), args.steps, 3)
     n_launch = n_layers * 2
     pass_bytes = wl.bytes_per_layer() * n_layers
     # DRAM bytes per launch from the ncu capture summarised in profiles/bgmv_fused_cfg1_ncu.md
@@ -335,6 +336,9 @@ def main():
         "shrink_half": {"achieved": shr_bytes / (ms_shr * 1e-3) / 1e9, "frac": shr_bytes / (ms_shr * 1e-3) / 1e9 / peak,
                         "us_per_launch": ms_shr * 1e3 / n_launch},
         "plan_us": us_plan,
+        # optional mode with the reference's `q += q_lora` rounding (delta rounded, then a 16-bit add)
+        "delta_then_add_mode": {"achieved": pass_bytes / (ms_dta * 1e-3) / 1e9,
+                                "frac": pass_bytes / (ms_dta * 1e-3) / 1e9 / peak, "us_per_launch": ms_dta * 1e3 / n_launch},
         "whole_pass": {"bytes": pass_bytes, "achieved": pass_bytes / (ms * 1e-3) / 1e9,
                        "frac": pass_bytes / (ms * 1e-3) / 1e9 / peak},
     }

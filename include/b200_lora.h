@@ -52,7 +52,13 @@ enum {
     B200_LORA_NO_TENSOR = 2,   /* keep tall segments on the BGMV kernels too (no tcgen05 tiles) */
     B200_LORA_ONLY_SHRINK = 4, /* tensor parallel / profiling: run only the shrink half (v is left in the workspace) */
     B200_LORA_ONLY_EXPAND = 8, /* profiling: run only the expand half on the workspace's current v */
-    B200_LORA_TWO_KERNELS = 16 /* run shrink and expand as two launches instead of the fused kernel */
+    B200_LORA_TWO_KERNELS = 16, /* run shrink and expand as two launches instead of the fused kernel */
+    B200_LORA_DELTA_THEN_ADD = 32 /* 16-bit y only: round the delta to the I/O type and add it to y in that
+                                   type, as the reference's `q += q_lora` does
+                                   (lightllm/models/llama/layer_infer/transformer_layer_infer.py:160-170).
+                                   Identical to the default when y starts at zero, which is how the
+                                   reference calls the op (lora_gpu.py:137); otherwise a second rounding.
+                                   Applies to the TMA BGMV kernels; other paths ignore it. */
 };
 
 /* The adapter table shared by the projections of one layer.

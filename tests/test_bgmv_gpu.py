@@ -127,3 +127,20 @@ def test_errors_are_raised_not_swallowed():
         batch.set_ids(c.ids_dev, c.pool).apply([(c.x, y, c.pool)], 5)       # layer out of range
     with pytest.raises(ValueError):
         L.add_lora_bgmv(y.cpu(), c.x.cpu(), c.pool.wa.cpu(), c.pool.wb.cpu(), c.ids_dev.cpu(), 0, 1.0)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_delta_then_add_mode(dtype):
+    """The reference adds the 16-bit delta to the projection in 16-bit arithmetic (q += q_lora)."""
+    c = Case(70, 12, 1024, 768, [8, 16, 32, 64], dtype, seed=77, zipf=1.0)
+    # y starting at zero (how the reference calls the op): identical to the default mode
+    assert torch.equal(c.run(1, flags=L.DELTA_THEN_ADD), c.run(1))
+    # y starting elsewhere: round(delta) added in the I/O type, the oracle's delta_then_add
+    g = torch.Generator().manual_seed(3)
+    y0 = torch.randn(c.T, c.h_out, generator=g).to(c.tdt).cuda()
+    got = c.run(1, y0=y0, flags=L.DELTA_THEN_ADD).double().cpu().numpy()
+    delta = O.round_to(c.oracle_delta(1), dtype)
+    want = O.delta_then_add(y0.double().cpu().numpy(), delta, dtype)
+    ulp = 2.0 ** (-10 if dtype == "fp16" else -7)
+    assert np.abs(got - want).max() <= ulp * np.abs(want).max()
+    assert (got != want).mean() < 0.02          # only ties of the delta's own rounding may differ
