@@ -53,7 +53,7 @@ bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t 
                    uint32_t box_rows, CUtensorMapSwizzle swizzle, uint64_t pitch = 0) {
     if (pitch == 0) pitch = inner;
     struct Entry { const void* base; uint64_t inner, rows, pitch; uint32_t bi, br; int sw; CUtensorMap map; };
-    static Entry cache[64];
+    static Entry cache[256];
     static int n_cached = 0, next = 0;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
@@ -75,8 +75,8 @@ bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t 
         return false;
     Entry& e = cache[next];
     e.base = base; e.inner = inner; e.rows = rows; e.pitch = pitch; e.bi = box_inner; e.br = box_rows; e.sw = (int)swizzle; e.map = m;
-    next = (next + 1) % 64;
-    if (n_cached < 64) ++n_cached;
+    next = (next + 1) % 256;
+    if (n_cached < 256) ++n_cached;
     *out = m;
     return true;
 }

@@ -32,20 +32,24 @@
 // reference (lightllm/models/lora_gpu.py:138,150,162), pools as at :33-40.
 #include "lora_common.cuh"
 
-// Optional cycle accounting for tuning (-DB200_LORA_TRACE): CTA 0 adds the cycles its producer
-// lane and its first consumer thread spend in each phase to workspace pad words.
-#ifdef B200_LORA_TRACE
-#define TRACE_DECL long long tr_t0 = clock64(); long long tr_acc[6] = {0, 0, 0, 0, 0, 0};
-#define TRACE_MARK(i) { long long tr_t1 = clock64(); tr_acc[i] += tr_t1 - tr_t0; tr_t0 = tr_t1; }
-#define TRACE_FLUSH(cond, base) if ((cond) && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) atomicAdd(&ws.ctl->pad[(base) + i], (unsigned)(tr_acc[i] >> 4)); }
-#define TRACE_ARGS , long long& tr_t0, long long (&tr_acc)[6]
-#define TRACE_PASS , tr_t0, tr_acc
+#ifdef B200_LORA_TIMELINE
+// Tuning aid (never in the shipped build): consumer thread 0 of every CTA stamps each item.
+__device__ unsigned long long g_timeline[512][96][12];
+__device__ int g_tl_slot;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+extern "C" int b200_lora_debug_timeline(void* host) { return (int)cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)); }
+#define TL(slot, k, v) { if (tid == 0 && (slot) < 96 && blockIdx.x < 512) g_timeline[blockIdx.x][slot][k] = (v); }
+// clock stamp k of the item the calling consumer is working on (slot kept in a register by the loop)
+#define TLC(k) { if (tid == 0 && tl_slot < 96 && blockIdx.x < 512) g_timeline[blockIdx.x][tl_slot][k] = (unsigned long long)clock64(); }
+#define TLC_ARG , int tl_slot
+#define TLC_PASS , n + 1
+#define TLN(k) { const int tl_slot = n + 1; TLC(k) }
 #else
-#define TRACE_DECL
-#define TRACE_MARK(i)
-#define TRACE_FLUSH(cond, base)
-#define TRACE_ARGS
-#define TRACE_PASS
+#define TL(slot, k, v)
+#define TLC(k)
+#define TLC_ARG
+#define TLC_PASS
+#define TLN(k)
 #endif
 
 namespace b200lora {
@@ -65,7 +69,7 @@ constexpr int kWTile = 16384;                     // weight tile of one unit
 constexpr int kXPad = 64;                         // bytes added to an x-tile row (bank spread)
 constexpr int kXBytes = 8 * (512 * 2 + kXPad);
 constexpr int kShrinkStage = kWTile + kXBytes;
-constexpr int kYPad = 16;
+constexpr int kYPad = 32;                        // y-tile rows 32 bytes apart modulo 128: no bank conflicts
 constexpr int kYBytes = 8 * (512 * 2 + kYPad);
 constexpr int kVPitch = 72;                       // floats per token row of the v tile
 constexpr int kVBytes = 8 * kVPitch * 4;
@@ -243,7 +247,7 @@ __device__ __forceinline__ void shrink_produce(const ApplyParams& p, const Item&
 // warps = (1, 2 or 4 row blocks) x (8, 4 or 2 slices of the unit's columns); a warp adds 4 MMAs
 // per unit into four independent accumulators that live across the units of one run.
 template <typename T>
-__device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid) {
+__device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid TLC_ARG) {
     const int lane = tid & 31, warp = tid >> 5;
     const int r = m.u.rank;
     const int MB = r >= 16 ? r / 16 : 1;                   // 16-row blocks: 1, 1, 2, 4
@@ -254,6 +258,7 @@ __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned cha
     const int g = lane >> 2, t = lane & 3;
     const unsigned char* xrow = stage + kWTile + g * (kc_cols * 2 + kXPad) + t * 16;
     const bool two = r >= 16;                              // rank 8 has no rows 8..15
+    TLC(6)
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb) {                        // every warp owns two 32-column blocks
         const int col = (kslot * 2 + kb) * 32;
@@ -268,6 +273,7 @@ __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned cha
             Mma<T>::run(acc[2 * kb + 1], w.z, u.z, w.w, u.w, xb.z, xb.w);
         }
     }
+    TLC(7)
 }
 
 // One run = consecutive units of one (projection, work segment) in this CTA.
@@ -401,7 +407,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         if (pw >= n_local) return;
         Cursor cur = cursor_at(p, first + pw, n_units, false);
         int rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
-        TRACE_DECL
         for (int n = pw; n < n_local; n += kProdWarps) {
             Cursor nxt = cur;
 #pragma unroll
@@ -411,18 +416,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, false);
-            TRACE_MARK(0)
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 1);
-            TRACE_MARK(1)
             publish_meta(&meta[n % kMetaSlots], rec, it, lane);
             const unsigned full = smem_u32(&bars[s]);
             if (it.valid) shrink_produce<T>(p, it, rec, smem_u32(smem + s * kShrinkStage), full, lane);
             else if (lane == 0) mbar_arrive(full);
             cur = nxt;
             rec = rec_nxt;
-            TRACE_MARK(2)
         }
-        TRACE_FLUSH(lane == 0, 0)
         return;
     }
 
@@ -435,47 +436,44 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     Run run;
     run.proj = -1; run.wseg = -1; run.count = 0;
     run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
-    TRACE_DECL
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
-        TRACE_MARK(0)
         mbar_wait(smem_u32(&bars[s]), ph, err, 2);
-        TRACE_MARK(1)
         const Meta& m = meta[n % kMetaSlots];
         if (m.valid) {
             if (m.proj != run.proj || m.u.wseg != run.wseg) {
                 if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid);
-                TRACE_MARK(3)
                 run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
                 run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
             }
-            shrink_consume<T>(m, smem + s * kShrinkStage, acc, tid);
+            shrink_consume<T>(m, smem + s * kShrinkStage, acc, tid TLC_PASS);
             ++run.count;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));      // this warp is done with the stage
-        TRACE_MARK(2)
     }
     if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid);
-    TRACE_MARK(3)
-    TRACE_FLUSH(tid == 0, 5)
 }
 
 // =============================================================================================
 // expand
 // =============================================================================================
+// `parts` bit 0: the barrier's byte count, the weight tile and the y rows (none of which depend
+// on the shrink half); bit 1: the rows of the intermediate v.
 template <typename T>
 __device__ __forceinline__ void expand_produce(const ApplyParams& p, const WorkspaceView& ws, const Item& m, int rec,
-                                               unsigned stage, unsigned bar, int lane) {
+                                               unsigned stage, unsigned bar, int lane, int parts = 3) {
     const ProjArgs& pj = p.proj[m.proj];
     const int r = m.rank;
     const int jc = kSuper / n_sub(r);
     const unsigned w_bytes = m.width_ok * r * 2;
     const unsigned y_bytes = (p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD)) ? 0u : m.width_ok * 2;
     const unsigned v_bytes = r * 4;
-    if (lane == 0) mbar_arrive_expect_tx(bar, w_bytes + m.ntok * (y_bytes + v_bytes));
-    __syncwarp();
+    if (parts & 1) {
+        if (lane == 0) mbar_arrive_expect_tx(bar, w_bytes + m.ntok * (y_bytes + v_bytes));
+        __syncwarp();
+    }
     // one instruction: lane 0 the weight tile, lanes 8..15 the y rows, lanes 16..23 the v rows
     const int tok = __shfl_sync(0xffffffffu, rec, 8 + (lane & 7));
     unsigned dst = 0, bytes = 0;
@@ -483,141 +481,188 @@ __device__ __forceinline__ void expand_produce(const ApplyParams& p, const Works
     if (lane == 0) {
         dst = stage;
         src = reinterpret_cast<const T*>(pj.wb) + (item_row0(p, m) * (long long)pj.h_out + (long long)m.c0 * r);
-        bytes = w_bytes;
+        bytes = (parts & 1) ? w_bytes : 0u;
     } else if (lane >= 8 && lane < 8 + m.ntok) {
         dst = stage + kWTile + (lane - 8) * (jc * 2 + kYPad);
         src = reinterpret_cast<const T*>(pj.y) + (long long)tok * pj.ldy + m.c0;
-        bytes = y_bytes;
+        bytes = (parts & 1) ? y_bytes : 0u;
     } else if (lane >= 16 && lane < 16 + m.ntok) {
         dst = stage + kWTile + kYBytes + (lane - 16) * (kVPitch * 4);
         src = ws.v + ((size_t)m.proj * p.cap + m.start + (lane - 16)) * kMaxRank;
-        bytes = v_bytes;
+        bytes = (parts & 2) ? v_bytes : 0u;
     }
     if (bytes) bulk_g2s(dst, src, bytes, bar);
 }
 
-// hi/lo split of two fp32 values into packed 16-bit pairs
+// One packed 16-bit pair of the hi halves (the values rounded to T) or of the lo halves (what
+// the rounding dropped) of two fp32 values.
 template <typename T>
-__device__ __forceinline__ void split2(float v0, float v1, unsigned& hi, unsigned& lo) {
+__device__ __forceinline__ unsigned hl_pack(float v0, float v1, bool lo) {
     const float h0 = Cvt<T>::round1(v0), h1 = Cvt<T>::round1(v1);
-    hi = Cvt<T>::pack2(h0, h1);
-    lo = Cvt<T>::pack2(v0 - h0, v1 - h1);
+    return lo ? Cvt<T>::pack2(v0 - h0, v1 - h1) : Cvt<T>::pack2(h0, h1);
 }
 
-// R = rank class.  The MMA's M rows 0..7 hold the hi halves of the tokens' intermediate and rows
-// 8..15 the lo halves, so one MMA yields both products.  Thread (g, t) owns, for token g and
-// output rows (8*block + 2t, +1):
+// R = rank class.  The weight tile is the MMA's A operand: 16 output columns (M) by 16 rank
+// indices (K, in a fixed permutation that lets a thread fetch its fragments with one wide load
+// per row).  The N columns are the tokens: column 2q holds the hi half of token q's
+// intermediate and column 2q+1 the lo half, so one MMA serves four tokens and a second one,
+// issued only for units of more than four tokens, serves tokens 4..7.  Thread (g, t) ends up
+// with the hi and lo products of token t for output columns g and g + 8 of the block.
 //   R=64: chunks 2t and 2t+1 of each 128-byte weight row (4 MMA k-steps)
 //   R=32: chunk t of each 64-byte row (2 k-steps);  R=16: 8 bytes (1 k-step);  R=8: 4 bytes.
-// All of a warp's MMAs are issued before any result is used.
+// A warp owns NBW consecutive 16-column blocks and, for a staged 16-bit y, writes its own
+// columns back, so the consumer warps never meet at a barrier.
 template <typename T, int R>
-__device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid TRACE_ARGS) {
-    constexpr int CALLS = R == 64 ? 4 : R == 32 ? 2 : 1;
+__device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid TLC_ARG) {
+    constexpr int KS = R == 64 ? 4 : R == 32 ? 2 : 1;
     constexpr int JC = kSuper / (R <= 16 ? 4 : R / 4);
-    constexpr int NBW = JC / 8 / kConsWarps;               // 8-row blocks per warp: 8, 8, 4, 2
+    constexpr int NBW = JC / 16 / kConsWarps;              // 16-column blocks per warp: 4, 4, 2, 1
     const ProjArgs& pj = p.proj[m.proj];
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int ntok = m.u.ntok;
+    const int ngrp = ntok > 4 ? 2 : 1;
     const float scale = m.u.scale;
-    const float* vt = reinterpret_cast<const float*>(stage + kWTile + kYBytes) + g * kVPitch;
+    const bool lo_half = (g & 1) != 0;
 
-    unsigned ah[CALLS][2], al[CALLS][2];
+    // B fragments of token (g >> 1) + 4 * group, hi or lo half by the parity of g
+    unsigned bf[2][KS][2];
 #pragma unroll
-    for (int c = 0; c < CALLS; ++c) { ah[c][0] = ah[c][1] = al[c][0] = al[c][1] = 0u; }
-    if (g < ntok) {
+    for (int grp = 0; grp < 2; ++grp) {
+#pragma unroll
+        for (int k = 0; k < KS; ++k) bf[grp][k][0] = bf[grp][k][1] = 0u;
+        const int q = (g >> 1) + 4 * grp;
+        if (q < ntok) {
+            const float* vt = reinterpret_cast<const float*>(stage + kWTile + kYBytes) + q * kVPitch;
+            if constexpr (R == 64) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const float4 lo4 = *reinterpret_cast<const float4*>(vt + (2 * t + c) * 8);
+                    const float4 hi4 = *reinterpret_cast<const float4*>(vt + (2 * t + c) * 8 + 4);
+                    bf[grp][2 * c][0] = hl_pack<T>(lo4.x, lo4.y, lo_half);
+                    bf[grp][2 * c][1] = hl_pack<T>(lo4.z, lo4.w, lo_half);
+                    bf[grp][2 * c + 1][0] = hl_pack<T>(hi4.x, hi4.y, lo_half);
+                    bf[grp][2 * c + 1][1] = hl_pack<T>(hi4.z, hi4.w, lo_half);
+                }
+            } else if constexpr (R == 32) {
+                const float4 lo4 = *reinterpret_cast<const float4*>(vt + t * 8);
+                const float4 hi4 = *reinterpret_cast<const float4*>(vt + t * 8 + 4);
+                bf[grp][0][0] = hl_pack<T>(lo4.x, lo4.y, lo_half);
+                bf[grp][0][1] = hl_pack<T>(lo4.z, lo4.w, lo_half);
+                bf[grp][1][0] = hl_pack<T>(hi4.x, hi4.y, lo_half);
+                bf[grp][1][1] = hl_pack<T>(hi4.z, hi4.w, lo_half);
+            } else if constexpr (R == 16) {
+                const float4 v4 = *reinterpret_cast<const float4*>(vt + t * 4);
+                bf[grp][0][0] = hl_pack<T>(v4.x, v4.y, lo_half);
+                bf[grp][0][1] = hl_pack<T>(v4.z, v4.w, lo_half);
+            } else {
+                const float2 v2 = *reinterpret_cast<const float2*>(vt + t * 2);
+                bf[grp][0][0] = hl_pack<T>(v2.x, v2.y, lo_half);
+            }
+        }
+    }
+
+    TLC(6)
+    const int jbase = warp * NBW * 16;
+    float acc[NBW][2][4];
+#pragma unroll
+    for (int nb = 0; nb < NBW; ++nb) {
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) acc[nb][grp][0] = acc[nb][grp][1] = acc[nb][grp][2] = acc[nb][grp][3] = 0.f;
+        const unsigned char* w0 = stage + (jbase + nb * 16 + g) * (R * 2);   // output column g of the block
+        const unsigned char* w1 = w0 + 8 * (R * 2);                          // output column g + 8
+        unsigned a[KS][4];
         if constexpr (R == 64) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const float4 lo4 = *reinterpret_cast<const float4*>(vt + (2 * t + c) * 8);
-                const float4 hi4 = *reinterpret_cast<const float4*>(vt + (2 * t + c) * 8 + 4);
-                split2<T>(lo4.x, lo4.y, ah[2 * c][0], al[2 * c][0]);
-                split2<T>(lo4.z, lo4.w, ah[2 * c][1], al[2 * c][1]);
-                split2<T>(hi4.x, hi4.y, ah[2 * c + 1][0], al[2 * c + 1][0]);
-                split2<T>(hi4.z, hi4.w, ah[2 * c + 1][1], al[2 * c + 1][1]);
+                const uint4 r0 = *reinterpret_cast<const uint4*>(w0 + (2 * t + c) * 16);
+                const uint4 r1 = *reinterpret_cast<const uint4*>(w1 + (2 * t + c) * 16);
+                a[2 * c][0] = r0.x; a[2 * c][1] = r1.x; a[2 * c][2] = r0.y; a[2 * c][3] = r1.y;
+                a[2 * c + 1][0] = r0.z; a[2 * c + 1][1] = r1.z; a[2 * c + 1][2] = r0.w; a[2 * c + 1][3] = r1.w;
             }
         } else if constexpr (R == 32) {
-            const float4 lo4 = *reinterpret_cast<const float4*>(vt + t * 8);
-            const float4 hi4 = *reinterpret_cast<const float4*>(vt + t * 8 + 4);
-            split2<T>(lo4.x, lo4.y, ah[0][0], al[0][0]);
-            split2<T>(lo4.z, lo4.w, ah[0][1], al[0][1]);
-            split2<T>(hi4.x, hi4.y, ah[1][0], al[1][0]);
-            split2<T>(hi4.z, hi4.w, ah[1][1], al[1][1]);
+            const uint4 r0 = *reinterpret_cast<const uint4*>(w0 + t * 16);
+            const uint4 r1 = *reinterpret_cast<const uint4*>(w1 + t * 16);
+            a[0][0] = r0.x; a[0][1] = r1.x; a[0][2] = r0.y; a[0][3] = r1.y;
+            a[1][0] = r0.z; a[1][1] = r1.z; a[1][2] = r0.w; a[1][3] = r1.w;
         } else if constexpr (R == 16) {
-            const float4 v4 = *reinterpret_cast<const float4*>(vt + t * 4);
-            split2<T>(v4.x, v4.y, ah[0][0], al[0][0]);
-            split2<T>(v4.z, v4.w, ah[0][1], al[0][1]);
+            const uint2 r0 = *reinterpret_cast<const uint2*>(w0 + t * 8);
+            const uint2 r1 = *reinterpret_cast<const uint2*>(w1 + t * 8);
+            a[0][0] = r0.x; a[0][1] = r1.x; a[0][2] = r0.y; a[0][3] = r1.y;
         } else {
-            const float2 v2 = *reinterpret_cast<const float2*>(vt + t * 2);
-            split2<T>(v2.x, v2.y, ah[0][0], al[0][0]);
+            a[0][0] = *reinterpret_cast<const unsigned*>(w0 + t * 4);
+            a[0][1] = *reinterpret_cast<const unsigned*>(w1 + t * 4);
+            a[0][2] = a[0][3] = 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < KS; ++k) Mma<T>::run(acc[nb][0], a[k][0], a[k][1], a[k][2], a[k][3], bf[0][k][0], bf[0][k][1]);
+        if (ngrp == 2) {
+#pragma unroll
+            for (int k = 0; k < KS; ++k) Mma<T>::run(acc[nb][1], a[k][0], a[k][1], a[k][2], a[k][3], bf[1][k][0], bf[1][k][1]);
         }
     }
 
-    TRACE_MARK(2)
-    const int jbase = warp * NBW * 8;
-    float acc[NBW][CALLS][4];
-#pragma unroll
-    for (int nb = 0; nb < NBW; ++nb) {
-#pragma unroll
-        for (int c = 0; c < CALLS; ++c) { acc[nb][c][0] = acc[nb][c][1] = acc[nb][c][2] = acc[nb][c][3] = 0.f; }
-        const unsigned char* wr = stage + (jbase + nb * 8 + g) * (R * 2);    // this thread's weight row (N index g)
-        if constexpr (R == 64) {
-            const uint4 w0 = *reinterpret_cast<const uint4*>(wr + (2 * t) * 16);
-            const uint4 w1 = *reinterpret_cast<const uint4*>(wr + (2 * t + 1) * 16);
-            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], ah[0][1], al[0][1], w0.x, w0.y);
-            Mma<T>::run(acc[nb][1], ah[1][0], al[1][0], ah[1][1], al[1][1], w0.z, w0.w);
-            Mma<T>::run(acc[nb][2], ah[2][0], al[2][0], ah[2][1], al[2][1], w1.x, w1.y);
-            Mma<T>::run(acc[nb][3], ah[3][0], al[3][0], ah[3][1], al[3][1], w1.z, w1.w);
-        } else if constexpr (R == 32) {
-            const uint4 w0 = *reinterpret_cast<const uint4*>(wr + t * 16);
-            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], ah[0][1], al[0][1], w0.x, w0.y);
-            Mma<T>::run(acc[nb][1], ah[1][0], al[1][0], ah[1][1], al[1][1], w0.z, w0.w);
-        } else if constexpr (R == 16) {
-            const uint2 w0 = *reinterpret_cast<const uint2*>(wr + t * 8);
-            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], ah[0][1], al[0][1], w0.x, w0.y);
-        } else {
-            const unsigned w0 = *reinterpret_cast<const unsigned*>(wr + t * 4);
-            Mma<T>::run(acc[nb][0], ah[0][0], al[0][0], 0u, 0u, w0, 0u);
-        }
-    }
-    TRACE_MARK(3)
-    // y[token g][j, j+1] += scale * (hi + lo products)
+    TLC(7)
+    // Token t (+4): hi + lo products for columns g and g + 8.  Lanes g and g ^ 1 swap one value
+    // so that each ends up with two adjacent columns: (g, g+1) for even g, (g+7, g+8) for odd g.
     unsigned char* ysb = stage + kWTile;
     constexpr int ypitch = JC * 2 + kYPad;
+    const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
 #pragma unroll
     for (int nb = 0; nb < NBW; ++nb) {
-        float s0 = 0.f, s1 = 0.f;
+        const int jblk = jbase + nb * 16;
 #pragma unroll
-        for (int c = 0; c < CALLS; ++c) { s0 += acc[nb][c][0] + acc[nb][c][2]; s1 += acc[nb][c][1] + acc[nb][c][3]; }
-        const int j = jbase + nb * 8 + 2 * t;
-        if (g < ntok && j < m.width_ok) {
-            const float d0 = scale * s0, d1 = scale * s1;
-            if (p.y_f32) {
-                float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + (long long)m.u.tok[g] * pj.ldy + m.c0 + j);
-                float2 yv = *yp;
-                yv.x += d0; yv.y += d1;
-                *yp = yv;
-            } else if (p.flags & B200_LORA_DELTA_THEN_ADD) {
-                // the delta is rounded to the I/O type and added to y in that type, two outputs
-                // per reduction, straight in global memory: no y tile, no write-back
-                T* yp = reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[g] * pj.ldy + m.c0 + j;
-                const unsigned d = Cvt<T>::pack2(d0, d1);
-                if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
-                else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
-            } else {
-                unsigned* yp = reinterpret_cast<unsigned*>(ysb + g * ypitch + j * 2);
-                const unsigned w = *yp;
-                float lo, hi;
-                if (Cvt<T>::is_bf16) {
-                    lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xffff0000u);
-                } else {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-                    lo = f.x; hi = f.y;
+        for (int grp = 0; grp < 2; ++grp) {
+            if (grp < ngrp) {
+                const float c_lo = scale * (acc[nb][grp][0] + acc[nb][grp][1]);
+                const float c_hi = scale * (acc[nb][grp][2] + acc[nb][grp][3]);
+                const float got = __shfl_xor_sync(0xffffffffu, lo_half ? c_lo : c_hi, 4);
+                const float d0 = lo_half ? got : c_lo, d1 = lo_half ? c_hi : got;
+                const int j = jblk + (lo_half ? g + 7 : g);
+                const int q = t + 4 * grp;
+                if (q < ntok && jblk < m.width_ok) {
+                    if (p.y_f32) {
+                        float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + (long long)m.u.tok[q] * pj.ldy + m.c0 + j);
+                        float2 yv = *yp;
+                        yv.x += d0; yv.y += d1;
+                        *yp = yv;
+                    } else if (!staged) {
+                        // the delta is rounded to the I/O type and added to y in that type, two
+                        // outputs per reduction, straight in global memory: no y tile, no write-back
+                        T* yp = reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[q] * pj.ldy + m.c0 + j;
+                        const unsigned d = Cvt<T>::pack2(d0, d1);
+                        if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
+                        else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
+                    } else {
+                        unsigned* yp = reinterpret_cast<unsigned*>(ysb + q * ypitch + j * 2);
+                        const unsigned w = *yp;
+                        float lo, hi;
+                        if (Cvt<T>::is_bf16) {
+                            lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xffff0000u);
+                        } else {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+                            lo = f.x; hi = f.y;
+                        }
+                        *yp = Cvt<T>::pack2(lo + d0, hi + d1);
+                    }
                 }
-                *yp = Cvt<T>::pack2(lo + d0, hi + d1);
             }
         }
     }
+    TLC(8)
+    if (staged) {
+        // the warp writes its own columns of the updated y tile back, 16 bytes per lane
+        __syncwarp();
+        constexpr int CPR = NBW * 2;                       // 16-byte chunks per token row: 8, 8, 4, 2
+        if (jbase < m.width_ok) {
+            for (int idx = lane; idx < ntok * CPR; idx += 32) {
+                const int row = idx / CPR, c = idx % CPR;
+                const uint4 val = *reinterpret_cast<const uint4*>(ysb + row * ypitch + jbase * 2 + c * 16);
+                *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + jbase + c * 8) = val;
+            }
+        }
+    }
+    TLC(9)
 }
 
 template <typename T>
@@ -655,7 +700,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         if (pw >= n_local) return;
         Cursor cur = cursor_at(p, first + pw, n_units, true);
         int rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
-        TRACE_DECL
         for (int n = pw; n < n_local; n += kProdWarps) {
             Cursor nxt = cur;
 #pragma unroll
@@ -665,59 +709,34 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, true);
-            TRACE_MARK(0)
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
-            TRACE_MARK(1)
             publish_meta(&meta[n % kMetaSlots], rec, it, lane);
             const unsigned full = smem_u32(&bars[s]);
             if (it.valid) expand_produce<T>(p, ws, it, rec, smem_u32(smem + s * kExpandStage), full, lane);
             else if (lane == 0) mbar_arrive(full);
             cur = nxt;
             rec = rec_nxt;
-            TRACE_MARK(2)
         }
-        TRACE_FLUSH(lane == 0, 0)
         return;
     }
 
-    TRACE_DECL
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
-        TRACE_MARK(0)
         mbar_wait(smem_u32(&bars[s]), ph, err, 4);
-        TRACE_MARK(1)
         const Meta& m = meta[n % kMetaSlots];
         unsigned char* stage = smem + s * kExpandStage;
         if (m.valid) {
             switch (m.u.rank) {
-                case 8:  expand_consume<T, 8>(p, m, stage, tid TRACE_PASS); break;
-                case 16: expand_consume<T, 16>(p, m, stage, tid TRACE_PASS); break;
-                case 32: expand_consume<T, 32>(p, m, stage, tid TRACE_PASS); break;
-                default: expand_consume<T, 64>(p, m, stage, tid TRACE_PASS); break;
-            }
-        }
-        TRACE_MARK(4)
-        const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
-        if (staged) cons_sync();
-        if (m.valid && staged) {
-            // coalesced write-back of the updated y tile, 16 bytes per thread
-            const ProjArgs& pj = p.proj[m.proj];
-            const int jc = kSuper / n_sub(m.u.rank);
-            const int cpt = jc / 8, cpt_shift = 31 - __clz(cpt);
-            const int c = tid & (cpt - 1), rstep = kConsThreads >> cpt_shift;
-            if (c * 8 < m.width_ok) {
-                for (int row = tid >> cpt_shift; row < m.u.ntok; row += rstep) {
-                    const uint4 val = *reinterpret_cast<const uint4*>(stage + kWTile + row * (jc * 2 + kYPad) + c * 16);
-                    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + c * 8) = val;
-                }
+                case 8:  expand_consume<T, 8>(p, m, stage, tid TLC_PASS); break;
+                case 16: expand_consume<T, 16>(p, m, stage, tid TLC_PASS); break;
+                case 32: expand_consume<T, 32>(p, m, stage, tid TLC_PASS); break;
+                default: expand_consume<T, 64>(p, m, stage, tid TLC_PASS); break;
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));     // one arrival per consumer warp
-        TRACE_MARK(0)
     }
-    TRACE_FLUSH(tid == 0, 5)
 }
 
 // =============================================================================================
@@ -752,7 +771,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    TL(0, 0, gtime())
     pdl_wait_prior();
+    TL(0, 1, gtime())
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -801,6 +822,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                 shrink_produce<T>(p, it, rec, stage, full, lane);
             } else {
                 const int wseg = __shfl_sync(0xffffffffu, rec, 4);
+                expand_produce<T>(p, ws, it, rec, stage, full, lane, 1);   // weights and y are in flight during the wait
                 if (lane == 0) {                               // v of this (projection, work segment) final?
                     const volatile unsigned* flag = &ws.ready[(size_t)it.proj * p.cap + wseg];
                     unsigned i = 0;
@@ -814,7 +836,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                     asm volatile("fence.proxy.async;" ::: "memory");   // generic writes of v -> bulk-copy reads
                 }
                 __syncwarp();
-                expand_produce<T>(p, ws, it, rec, stage, full, lane);
+                expand_produce<T>(p, ws, it, rec, stage, full, lane, 2);
             }
             // advance this warp's cursor by kProdWarps items and fetch the next record
             Cursor nxt = cur;
@@ -838,9 +860,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
         for (int n = 0; n < n_total; ++n) {
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
+            TL(n + 1, 0, gtime())
             mbar_wait(smem_u32(&bars[s]), ph, err, 2);
+            TL(n + 1, 1, gtime())
             const Meta& m = meta[n % kMetaSlots];
             const int kind = m.pad[0];
+            TL(n + 1, 3, (unsigned long long)(kind | (m.u.rank << 8) | (m.u.ntok << 16) | (m.valid << 24)))
+            TLN(4)
             unsigned char* stage = smem + s * kFusedStage;
             if (kind == kKindFlush) {
                 if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, ready_val);
@@ -852,38 +878,28 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                         run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
                         run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
                     }
-                    shrink_consume<T>(m, stage, acc, tid);
+                    shrink_consume<T>(m, stage, acc, tid TLC_PASS);
                     ++run.count;
                 }
             } else {
                 if (m.valid) {
                     switch (m.u.rank) {
-                        case 8:  expand_consume<T, 8>(p, m, stage, tid); break;
-                        case 16: expand_consume<T, 16>(p, m, stage, tid); break;
-                        case 32: expand_consume<T, 32>(p, m, stage, tid); break;
-                        default: expand_consume<T, 64>(p, m, stage, tid); break;
-                    }
-                }
-                const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
-                if (staged) cons_sync();
-                if (m.valid && staged) {
-                    const ProjArgs& pj = p.proj[m.proj];
-                    const int jc = kSuper / n_sub(m.u.rank);
-                    const int cpt = jc / 8, cpt_shift = 31 - __clz(cpt);
-                    const int c = tid & (cpt - 1), rstep = kConsThreads >> cpt_shift;
-                    if (c * 8 < m.width_ok) {
-                        for (int row = tid >> cpt_shift; row < m.u.ntok; row += rstep) {
-                            const uint4 val = *reinterpret_cast<const uint4*>(stage + kWTile + row * (jc * 2 + kYPad) + c * 16);
-                            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + c * 8) = val;
-                        }
+                        case 8:  expand_consume<T, 8>(p, m, stage, tid TLC_PASS); break;
+                        case 16: expand_consume<T, 16>(p, m, stage, tid TLC_PASS); break;
+                        case 32: expand_consume<T, 32>(p, m, stage, tid TLC_PASS); break;
+                        default: expand_consume<T, 64>(p, m, stage, tid TLC_PASS); break;
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));
+            TLN(10)
+            TL(n + 1, 2, gtime())
         }
     }
     __syncthreads();
+    TL(0, 2, gtime())
+    TL(0, 3, (unsigned long long)n_total)
     if (tid == 0) {                                            // the last CTA out advances the epoch
         __threadfence();
         const unsigned d = atomicAdd(&ws.ctl->done[0], 1u);
