@@ -43,12 +43,14 @@ extern "C" int b200_lora_debug_timeline(void* host) { return (int)cudaMemcpyFrom
 #define TLC(k) { if (tid == 0 && tl_slot < 96 && blockIdx.x < 512) g_timeline[blockIdx.x][tl_slot][k] = (unsigned long long)clock64(); }
 #define TLC_ARG , int tl_slot
 #define TLC_PASS , n + 1
+#define TLC_FWD , tl_slot
 #define TLN(k) { const int tl_slot = n + 1; TLC(k) }
 #else
 #define TL(slot, k, v)
 #define TLC(k)
 #define TLC_ARG
 #define TLC_PASS
+#define TLC_FWD
 #define TLN(k)
 #endif
 
@@ -140,36 +142,64 @@ template <> struct Mma<__nv_bfloat16> {
     }
 };
 
-__device__ __forceinline__ unsigned atom_add_acq_rel(unsigned* p, unsigned v) {
-    unsigned old;
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-    return old;
-}
-
-// Cursor over a CTA's contiguous range of items.  item -> (unit, projection, super-chunk) with
-// unit fastest, so consecutive items are consecutive sub-ranges of one work segment.
+// Cursor over a CTA's contiguous range of items.  The items are ordered projection by
+// projection, work segment by work segment, and inside a segment super-chunk by super-chunk and
+// sub-range by sub-range, so all units of one (projection, work segment) are neighbours: a CTA
+// usually sees whole segments, and the expand units it gets belong to the segments it shrank.
+// The plan's unit table holds one record per (work segment, sub-range), the records of a
+// segment next to each other and equal but for the sub-range, so any of them describes it.
 struct Cursor {
-    int unit, sp, proj, super;
+    int unit;       // first plan unit of the work segment
+    int sp, sub;    // super-chunk and sub-range inside the segment
+    int proj, super;
+    int ns;         // super-chunks of the projection in this list
+    int nsub_log;   // log2(sub-ranges per super-chunk): 2, 2, 3, 4 for rank 8, 16, 32, 64
 };
-__device__ __forceinline__ void cursor_split(const ApplyParams& p, bool expand, Cursor& c) {
-    int sp = c.sp, pi = 0;
+__device__ __forceinline__ int ns_of(const ApplyParams& p, int pi, bool expand) {
+    return expand ? p.proj[pi].n_super_out : p.proj[pi].n_super_in;
+}
+__device__ __forceinline__ int nsub_log_of(int rank) { return rank <= 16 ? 2 : rank <= 32 ? 3 : 4; }
+__device__ __forceinline__ int load_record(const int* unit_tab, int unit, int lane) {
+    return lane < 16 ? __ldg(unit_tab + (size_t)unit * 16 + lane) : 0;
+}
+// positions the cursor at item `it` and fetches the record of its work segment
+__device__ __forceinline__ Cursor cursor_at(const ApplyParams& p, int it, int n_units, bool expand, const int* unit_tab,
+                                            int lane, int& rec) {
+    Cursor c;
+    int local = it, pi = 0;
 #pragma unroll
-    for (int i = 0; i < kMaxProj; ++i) {
-        const int ns = expand ? p.proj[i].n_super_out : p.proj[i].n_super_in;
-        if (i < p.n_proj - 1 && pi == i && sp >= ns) { sp -= ns; pi = i + 1; }
+    for (int i = 0; i < kMaxProj - 1; ++i) {
+        const int cnt = n_units * ns_of(p, i, expand);
+        if (i < p.n_proj - 1 && pi == i && local >= cnt) { local -= cnt; pi = i + 1; }
     }
     c.proj = pi;
-    c.super = sp;
-}
-__device__ __forceinline__ Cursor cursor_at(const ApplyParams& p, int it, int n_units, bool expand) {
-    Cursor c;
-    c.unit = it % n_units;
-    c.sp = it / n_units;
-    cursor_split(p, expand, c);
+    c.ns = ns_of(p, pi, expand);
+    const int up = local / c.ns;                           // a unit of the item's segment
+    rec = load_record(unit_tab, up, lane);
+    c.nsub_log = nsub_log_of(__shfl_sync(0xffffffffu, rec, 1));
+    c.unit = up - (__shfl_sync(0xffffffffu, rec, 2) & 0xffff);
+    const int l2 = local - c.unit * c.ns;
+    c.sp = c.super = l2 >> c.nsub_log;
+    c.sub = l2 & ((1 << c.nsub_log) - 1);
     return c;
 }
-__device__ __forceinline__ void cursor_next(const ApplyParams& p, int n_units, bool expand, Cursor& c) {
-    if (++c.unit == n_units) { c.unit = 0; ++c.sp; cursor_split(p, expand, c); }
+// advances by `steps` items; fetches the new record whenever the work segment changes
+__device__ __forceinline__ void cursor_advance(const ApplyParams& p, int n_units, bool expand, const int* unit_tab, int lane,
+                                               int steps, Cursor& c, int& rec) {
+    for (int q = 0; q < steps; ++q) {
+        if (++c.sub < (1 << c.nsub_log)) continue;
+        c.sub = 0;
+        if (++c.sp < c.ns) { c.super = c.sp; continue; }
+        c.sp = c.super = 0;
+        c.unit += 1 << c.nsub_log;
+        if (c.unit >= n_units) {
+            c.unit = 0;
+            c.proj = min(c.proj + 1, p.n_proj - 1);
+            c.ns = ns_of(p, c.proj, expand);
+        }
+        rec = load_record(unit_tab, c.unit, lane);
+        c.nsub_log = nsub_log_of(__shfl_sync(0xffffffffu, rec, 1));
+    }
 }
 
 // What the producer derives for one item; every lane computes it from the broadcast record.
@@ -183,7 +213,7 @@ __device__ __forceinline__ Item make_item(const ApplyParams& p, int rec, const C
     it.adapter = __shfl_sync(0xffffffffu, rec, 0);
     it.rank = __shfl_sync(0xffffffffu, rec, 1);
     const int w2 = __shfl_sync(0xffffffffu, rec, 2);
-    it.sub = w2 & 0xffff;
+    it.sub = c.sub;
     it.ntok = (w2 >> 16) & 0xffff;
     it.start = __shfl_sync(0xffffffffu, rec, 5);
     const unsigned lo = (unsigned)__shfl_sync(0xffffffffu, rec, 6);
@@ -246,34 +276,41 @@ __device__ __forceinline__ void shrink_produce(const ApplyParams& p, const Item&
 // Weight rows are the M rows of the MMA (16 per block), the unit's tokens its N columns.  The 8
 // warps = (1, 2 or 4 row blocks) x (8, 4 or 2 slices of the unit's columns); a warp adds 4 MMAs
 // per unit into four independent accumulators that live across the units of one run.
-template <typename T>
+template <typename T, int R>
 __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid TLC_ARG) {
+    constexpr int MB = R >= 16 ? R / 16 : 1;               // 16-row blocks: 1, 1, 2, 4
+    constexpr int KSPLIT = kConsWarps / MB;                // 8, 8, 4, 2
+    constexpr int KC_COLS = R <= 16 ? 512 : R == 32 ? 256 : 128;
+    constexpr int NCB = KC_COLS / kBoxCols;
     const int lane = tid & 31, warp = tid >> 5;
-    const int r = m.u.rank;
-    const int MB = r >= 16 ? r / 16 : 1;                   // 16-row blocks: 1, 1, 2, 4
-    const int ksplit = kConsWarps / MB;                    // 8, 8, 4, 2
-    const int kc_cols = kSuper / n_sub(r);
-    const int ncb = kc_cols / kBoxCols;
-    const int kslot = warp % ksplit, mblk = warp / ksplit;
+    const int kslot = warp % KSPLIT, mblk = warp / KSPLIT;
     const int g = lane >> 2, t = lane & 3;
-    const unsigned char* xrow = stage + kWTile + g * (kc_cols * 2 + kXPad) + t * 16;
-    const bool two = r >= 16;                              // rank 8 has no rows 8..15
+    const unsigned char* xrow = stage + kWTile + g * (KC_COLS * 2 + kXPad) + t * 16;
     TLC(6)
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb) {                        // every warp owns two 32-column blocks
         const int col = (kslot * 2 + kb) * 32;
         if (col < m.width_ok) {
             const int cb = col >> 7, cin = col & 127;
-            const unsigned char* wbox = stage + ((mblk * 2) * ncb + cb) * kBoxBytes + g * 256 + cin * 2 + t * 16;
+            const unsigned char* wbox = stage + ((mblk * 2) * NCB + cb) * kBoxBytes + g * 256 + cin * 2 + t * 16;
             const uint4 xb = *reinterpret_cast<const uint4*>(xrow + col * 2);
             const uint4 w = *reinterpret_cast<const uint4*>(wbox);
             uint4 u = make_uint4(0u, 0u, 0u, 0u);
-            if (two) u = *reinterpret_cast<const uint4*>(wbox + ncb * kBoxBytes);
+            if (R >= 16) u = *reinterpret_cast<const uint4*>(wbox + NCB * kBoxBytes);   // rank 8 has no rows 8..15
             Mma<T>::run(acc[2 * kb], w.x, u.x, w.y, u.y, xb.x, xb.y);
             Mma<T>::run(acc[2 * kb + 1], w.z, u.z, w.w, u.w, xb.z, xb.w);
         }
     }
     TLC(7)
+}
+template <typename T>
+__device__ __forceinline__ void shrink_consume_any(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid TLC_ARG) {
+    switch (m.u.rank) {
+        case 8:  shrink_consume<T, 8>(m, stage, acc, tid TLC_FWD); break;
+        case 16: shrink_consume<T, 16>(m, stage, acc, tid TLC_FWD); break;
+        case 32: shrink_consume<T, 32>(m, stage, acc, tid TLC_FWD); break;
+        default: shrink_consume<T, 64>(m, stage, acc, tid TLC_FWD); break;
+    }
 }
 
 // One run = consecutive units of one (projection, work segment) in this CTA.
@@ -281,17 +318,86 @@ struct Run {
     int proj, wseg, start, ntok, rank, first_kc, count, n_chunks;
 };
 
-// Ends a run: cross-warp reduction, one split-K partial, arrival; folds if this arrival
-// completed the (projection, work segment).
+// release only: an acquiring atomic would hold back the thread's later loads until it returns
+__device__ __forceinline__ unsigned atom_add_release(unsigned* p, unsigned v) {
+    unsigned old;
+    asm volatile("atom.add.release.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// A published run whose arrival count has not been looked at yet (thread 0 holds `old`).
+struct Pending {
+    Run run;
+    unsigned old;
+    bool have;
+};
+
+// Looks at the arrival of a published run: the CTA whose arrival completed the (projection,
+// work segment) folds the partials in ascending k order into v and marks it ready.
+template <typename T>
+__device__ __forceinline__ void shrink_settle(const ApplyParams& p, const WorkspaceView& ws, Pending& pd, int* s_flag,
+                                              int tid, unsigned ready_val) {
+    if (!pd.have) return;
+    pd.have = false;
+    const Run& run = pd.run;
+    if (tid == 0) *s_flag = (pd.old + (unsigned)run.count == (unsigned)run.n_chunks) ? 1 : 0;
+    cons_sync();
+    const int last = *s_flag;
+    cons_sync();                                           // s_flag may be rewritten by the next settle
+    if (!last) return;
+    __threadfence();                                       // acquire side of the other CTAs' releasing arrivals
+    const int r = run.rank;
+    const int outs = run.ntok * r;
+    const int rshift = 31 - __clz(r);
+    const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
+    const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
+    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
+    const unsigned long long mask = *reinterpret_cast<volatile unsigned long long*>(&ws.masks[cidx]);
+    for (int idx = tid; idx < outs; idx += kConsThreads) {
+        const int pos = run.start + (idx >> rshift), i = idx & (r - 1);
+        const float* src = &ws.partial[((size_t)run.proj * p.cap + pos) * kMaxRank + i];
+        float s = 0.f;
+        unsigned long long mm = mask;
+        while (mm) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {                  // up to four loads in flight, summed in order
+                if (mm) {
+                    const int kc = __ffsll((long long)mm) - 1;
+                    mm &= mm - 1;
+                    v[j] = __ldcg(src + (size_t)kc * cstride);
+                }
+            }
+            s = (((s + v[0]) + v[1]) + v[2]) + v[3];
+        }
+        if (mid_round) s = Cvt<T>::round1(s);
+        ws.v[((size_t)run.proj * p.cap + pos) * kMaxRank + i] = s;
+    }
+    cons_sync();                                           // v written by all threads
+    if (tid == 0) {
+        ws.counters[cidx] = 0u;
+        ws.masks[cidx] = 0ull;
+        if (ready_val) st_release(&ws.ready[cidx], ready_val);     // v is final: let the expand units go
+        else __threadfence();
+    }
+}
+
+// Ends a run: cross-warp reduction, then v itself (the CTA saw every unit of the segment) or one
+// split-K partial and the arrival.  The arrival's return value is looked at by shrink_settle
+// when the next run ends, so nobody waits for the atomic.
 template <typename T>
 __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const WorkspaceView& ws, const Run& run,
-                                             float (&acc)[4][4], float* red, int* s_flag, int tid,
+                                             float (&acc)[4][4], float* red, int* s_flag, int tid, Pending& pd,
                                              unsigned ready_val = 0u) {
+    shrink_settle<T>(p, ws, pd, s_flag, tid, ready_val);
     const int lane = tid & 31, warp = tid >> 5;
     const int r = run.rank, rp = r + 4;
-    const int MB = r >= 16 ? r / 16 : 1;
-    const int ksplit = kConsWarps / MB;
-    const int kslot = warp % ksplit, mblk = warp / ksplit;
+    const int mb_log = r >= 64 ? 2 : r >= 32 ? 1 : 0;
+    const int ksplit = kConsWarps >> mb_log;
+    const int kslot = warp & (ksplit - 1), mblk = warp >> (3 - mb_log);
     const int g = lane >> 2, t = lane & 3;
     float c[4];
 #pragma unroll
@@ -321,51 +427,18 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         if (whole) ws.v[o] = mid_round ? Cvt<T>::round1(s) : s;
         else ws.partial[(size_t)run.first_kc * cstride + o] = s;
     }
-    cons_sync();                                           // partial written by all threads, red free again
-    const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
-    if (whole) {                                           // nothing to combine across CTAs
-        if (ready_val && tid == 0) {
-            __threadfence();
-            *reinterpret_cast<volatile unsigned*>(&ws.ready[cidx]) = ready_val;
-        }
-        return;
-    }
+    cons_sync();                                           // written by all threads, red free again
     if (tid == 0) {
-        atomicOr(&ws.masks[cidx], 1ull << run.first_kc);
-        const unsigned old = atom_add_acq_rel(&ws.counters[cidx], (unsigned)run.count);
-        *s_flag = (old + (unsigned)run.count == (unsigned)run.n_chunks) ? 1 : 0;
-    }
-    cons_sync();
-    if (*s_flag) {
-        // fold the marked slots in ascending k order
-        const unsigned long long mask = *reinterpret_cast<volatile unsigned long long*>(&ws.masks[cidx]);
-        for (int idx = tid; idx < outs; idx += kConsThreads) {
-            const int pos = run.start + (idx >> rshift), i = idx & (r - 1);
-            const float* src = &ws.partial[((size_t)run.proj * p.cap + pos) * kMaxRank + i];
-            float s = 0.f;
-            unsigned long long mm = mask;
-            while (mm) {
-                float v[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {              // up to four loads in flight, summed in order
-                    if (mm) {
-                        const int kc = __ffsll((long long)mm) - 1;
-                        mm &= mm - 1;
-                        v[j] = __ldcg(src + (size_t)kc * cstride);
-                    }
-                }
-                s = (((s + v[0]) + v[1]) + v[2]) + v[3];
-            }
-            if (mid_round) s = Cvt<T>::round1(s);
-            ws.v[((size_t)run.proj * p.cap + pos) * kMaxRank + i] = s;
+        const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
+        if (whole) {                                       // nothing to combine across CTAs
+            if (ready_val) st_release(&ws.ready[cidx], ready_val);
+            else __threadfence();
+        } else {
+            atomicOr(&ws.masks[cidx], 1ull << run.first_kc);   // no return value: a reduction, not waited for
+            pd.old = atom_add_release(&ws.counters[cidx], (unsigned)run.count);
         }
-        if (tid == 0) { ws.counters[cidx] = 0u; ws.masks[cidx] = 0ull; }
     }
-    cons_sync();                                           // s_flag may be rewritten by the next flush
-    if (ready_val && *s_flag && tid == 0) {                // v is final: let the expand units go
-        __threadfence();
-        *reinterpret_cast<volatile unsigned*>(&ws.ready[cidx]) = ready_val;
-    }
+    if (!whole) { pd.run = run; pd.have = true; }
 }
 
 template <typename T>
@@ -405,14 +478,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         // ---------------- producer warps ----------------
         const int pw = warp - kConsWarps;
         if (pw >= n_local) return;
-        Cursor cur = cursor_at(p, first + pw, n_units, false);
-        int rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
+        int rec;
+        Cursor cur = cursor_at(p, first + pw, n_units, false, pv.unit_tab, lane, rec);
         for (int n = pw; n < n_local; n += kProdWarps) {
-            Cursor nxt = cur;
-#pragma unroll
-            for (int q = 0; q < kProdWarps; ++q) cursor_next(p, n_units, false, nxt);
-            int rec_nxt = 0;                                   // next record: in flight during this item
-            if (n + kProdWarps < n_local && lane < 16) rec_nxt = __ldg(pv.unit_tab + (size_t)nxt.unit * 16 + lane);
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, false);
@@ -421,8 +489,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
             const unsigned full = smem_u32(&bars[s]);
             if (it.valid) shrink_produce<T>(p, it, rec, smem_u32(smem + s * kShrinkStage), full, lane);
             else if (lane == 0) mbar_arrive(full);
-            cur = nxt;
-            rec = rec_nxt;
+            if (n + kProdWarps < n_local) cursor_advance(p, n_units, false, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
         return;
     }
@@ -436,6 +503,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     Run run;
     run.proj = -1; run.wseg = -1; run.count = 0;
     run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
+    Pending pd;
+    pd.run = run; pd.old = 0u; pd.have = false;
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
@@ -443,17 +512,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         const Meta& m = meta[n % kMetaSlots];
         if (m.valid) {
             if (m.proj != run.proj || m.u.wseg != run.wseg) {
-                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid);
+                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd);
                 run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
                 run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
             }
-            shrink_consume<T>(m, smem + s * kShrinkStage, acc, tid TLC_PASS);
+            shrink_consume_any<T>(m, smem + s * kShrinkStage, acc, tid TLC_PASS);
             ++run.count;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));      // this warp is done with the stage
     }
-    if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid);
+    if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd);
+    shrink_settle<T>(p, ws, pd, s_flag, tid, 0u);
 }
 
 // =============================================================================================
@@ -513,7 +583,8 @@ __device__ __forceinline__ unsigned hl_pack(float v0, float v1, bool lo) {
 // A warp owns NBW consecutive 16-column blocks and, for a staged 16-bit y, writes its own
 // columns back, so the consumer warps never meet at a barrier.
 template <typename T, int R>
-__device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid TLC_ARG) {
+__device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid,
+                                               unsigned (&bf)[2][4][2], bool reuse TLC_ARG) {
     constexpr int KS = R == 64 ? 4 : R == 32 ? 2 : 1;
     constexpr int JC = kSuper / (R <= 16 ? 4 : R / 4);
     constexpr int NBW = JC / 16 / kConsWarps;              // 16-column blocks per warp: 4, 4, 2, 1
@@ -525,8 +596,9 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
     const float scale = m.u.scale;
     const bool lo_half = (g & 1) != 0;
 
-    // B fragments of token (g >> 1) + 4 * group, hi or lo half by the parity of g
-    unsigned bf[2][KS][2];
+    // B fragments of token (g >> 1) + 4 * group, hi or lo half by the parity of g; they are the
+    // same for every unit of one (projection, work segment), so consecutive units reuse them
+    if (!reuse) {
 #pragma unroll
     for (int grp = 0; grp < 2; ++grp) {
 #pragma unroll
@@ -560,6 +632,7 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
                 bf[grp][0][0] = hl_pack<T>(v2.x, v2.y, lo_half);
             }
         }
+    }
     }
 
     TLC(6)
@@ -608,42 +681,74 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
     unsigned char* ysb = stage + kWTile;
     constexpr int ypitch = JC * 2 + kYPad;
     const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
+    const int jl = jbase + (lo_half ? g + 7 : g);
+    float d0[NBW][2], d1[NBW][2];
 #pragma unroll
     for (int nb = 0; nb < NBW; ++nb) {
-        const int jblk = jbase + nb * 16;
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
+            d0[nb][grp] = d1[nb][grp] = 0.f;
             if (grp < ngrp) {
                 const float c_lo = scale * (acc[nb][grp][0] + acc[nb][grp][1]);
                 const float c_hi = scale * (acc[nb][grp][2] + acc[nb][grp][3]);
                 const float got = __shfl_xor_sync(0xffffffffu, lo_half ? c_lo : c_hi, 4);
-                const float d0 = lo_half ? got : c_lo, d1 = lo_half ? c_hi : got;
-                const int j = jblk + (lo_half ? g + 7 : g);
-                const int q = t + 4 * grp;
-                if (q < ntok && jblk < m.width_ok) {
-                    if (p.y_f32) {
-                        float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + (long long)m.u.tok[q] * pj.ldy + m.c0 + j);
-                        float2 yv = *yp;
-                        yv.x += d0; yv.y += d1;
-                        *yp = yv;
-                    } else if (!staged) {
-                        // the delta is rounded to the I/O type and added to y in that type, two
-                        // outputs per reduction, straight in global memory: no y tile, no write-back
-                        T* yp = reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[q] * pj.ldy + m.c0 + j;
-                        const unsigned d = Cvt<T>::pack2(d0, d1);
-                        if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
-                        else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp), "r"(d) : "memory");
+                d0[nb][grp] = lo_half ? got : c_lo;
+                d1[nb][grp] = lo_half ? c_hi : got;
+            }
+        }
+    }
+    const bool col_ok = jbase < m.width_ok;                // the warp's columns lie inside the matrix
+    if (staged) {
+        // all of the lane's y pairs are read before the first one is written back
+        unsigned yw[NBW][2];
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const unsigned* yp = reinterpret_cast<const unsigned*>(ysb + (t + 4 * grp) * ypitch + jl * 2);
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) yw[nb][grp] = (grp < ngrp) ? yp[nb * 8] : 0u;
+        }
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            if (grp < ngrp && t + 4 * grp < ntok && col_ok) {
+                unsigned* yp = reinterpret_cast<unsigned*>(ysb + (t + 4 * grp) * ypitch + jl * 2);
+#pragma unroll
+                for (int nb = 0; nb < NBW; ++nb) {
+                    float lo, hi;
+                    if (Cvt<T>::is_bf16) {
+                        lo = __uint_as_float(yw[nb][grp] << 16); hi = __uint_as_float(yw[nb][grp] & 0xffff0000u);
                     } else {
-                        unsigned* yp = reinterpret_cast<unsigned*>(ysb + q * ypitch + j * 2);
-                        const unsigned w = *yp;
-                        float lo, hi;
-                        if (Cvt<T>::is_bf16) {
-                            lo = __uint_as_float(w << 16); hi = __uint_as_float(w & 0xffff0000u);
-                        } else {
-                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-                            lo = f.x; hi = f.y;
-                        }
-                        *yp = Cvt<T>::pack2(lo + d0, hi + d1);
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&yw[nb][grp]));
+                        lo = f.x; hi = f.y;
+                    }
+                    yp[nb * 8] = Cvt<T>::pack2(lo + d0[nb][grp], hi + d1[nb][grp]);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const int q = t + 4 * grp;
+            if (grp < ngrp && q < ntok && col_ok) {
+                const long long yoff = (long long)m.u.tok[q] * pj.ldy + m.c0 + jl;
+                if (p.y_f32) {
+                    float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + yoff);
+                    float2 yv[NBW];
+#pragma unroll
+                    for (int nb = 0; nb < NBW; ++nb) yv[nb] = yp[nb * 8];
+#pragma unroll
+                    for (int nb = 0; nb < NBW; ++nb) {
+                        yv[nb].x += d0[nb][grp]; yv[nb].y += d1[nb][grp];
+                        yp[nb * 8] = yv[nb];
+                    }
+                } else {
+                    // the delta is rounded to the I/O type and added to y in that type, two outputs
+                    // per reduction, straight in global memory: no y tile, no write-back
+                    T* yp = reinterpret_cast<T*>(pj.y) + yoff;
+#pragma unroll
+                    for (int nb = 0; nb < NBW; ++nb) {
+                        const unsigned d = Cvt<T>::pack2(d0[nb][grp], d1[nb][grp]);
+                        if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
+                        else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
                     }
                 }
             }
@@ -698,14 +803,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
     if (warp >= kConsWarps) {
         const int pw = warp - kConsWarps;
         if (pw >= n_local) return;
-        Cursor cur = cursor_at(p, first + pw, n_units, true);
-        int rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
+        int rec;
+        Cursor cur = cursor_at(p, first + pw, n_units, true, pv.unit_tab, lane, rec);
         for (int n = pw; n < n_local; n += kProdWarps) {
-            Cursor nxt = cur;
-#pragma unroll
-            for (int q = 0; q < kProdWarps; ++q) cursor_next(p, n_units, true, nxt);
-            int rec_nxt = 0;
-            if (n + kProdWarps < n_local && lane < 16) rec_nxt = __ldg(pv.unit_tab + (size_t)nxt.unit * 16 + lane);
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, true);
@@ -714,12 +814,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             const unsigned full = smem_u32(&bars[s]);
             if (it.valid) expand_produce<T>(p, ws, it, rec, smem_u32(smem + s * kExpandStage), full, lane);
             else if (lane == 0) mbar_arrive(full);
-            cur = nxt;
-            rec = rec_nxt;
+            if (n + kProdWarps < n_local) cursor_advance(p, n_units, true, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
         return;
     }
 
+    unsigned bf[2][4][2];                                  // v fragments of the last (projection, work segment)
+    int bf_key = -1;
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
@@ -727,11 +828,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         const Meta& m = meta[n % kMetaSlots];
         unsigned char* stage = smem + s * kExpandStage;
         if (m.valid) {
+            const int key = m.proj * p.cap + m.u.wseg;
+            const bool reuse = key == bf_key;
+            bf_key = key;
             switch (m.u.rank) {
-                case 8:  expand_consume<T, 8>(p, m, stage, tid TLC_PASS); break;
-                case 16: expand_consume<T, 16>(p, m, stage, tid TLC_PASS); break;
-                case 32: expand_consume<T, 32>(p, m, stage, tid TLC_PASS); break;
-                default: expand_consume<T, 64>(p, m, stage, tid TLC_PASS); break;
+                case 8:  expand_consume<T, 8>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                case 16: expand_consume<T, 16>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                case 32: expand_consume<T, 32>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                default: expand_consume<T, 64>(p, m, stage, tid, bf, reuse TLC_PASS); break;
             }
         }
         __syncwarp();
@@ -792,9 +896,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
         // ---------------- producer warps (alternate items) ----------------
         const int pw = warp - kConsWarps;
         Cursor cur;
-        cur.unit = cur.sp = cur.proj = cur.super = 0;
+        cur.unit = cur.sp = cur.sub = cur.proj = cur.super = cur.ns = cur.nsub_log = 0;
         int rec = 0;
         bool have_a = false, have_b = false;
+        int polled = -1;                                       // (projection, work segment) last seen ready
         for (int n = pw; n < n_total; n += kProdWarps) {
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
@@ -808,8 +913,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                 continue;
             }
             const bool expand = n > nl_a;
-            if (!expand && !have_a) { cur = cursor_at(p, first_a + n, n_units, false); have_a = true; rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0; }
-            if (expand && !have_b) { cur = cursor_at(p, first_b + (n - nl_a - 1), n_units, true); have_b = true; rec = lane < 16 ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0; }
+            if (!expand && !have_a) { cur = cursor_at(p, first_a + n, n_units, false, pv.unit_tab, lane, rec); have_a = true; }
+            if (expand && !have_b) { cur = cursor_at(p, first_b + (n - nl_a - 1), n_units, true, pv.unit_tab, lane, rec); have_b = true; }
             const Item it = make_item(p, rec, cur, expand);
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, expand ? 3 : 1);
             publish_meta(slot, rec, it, lane);
@@ -823,8 +928,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
             } else {
                 const int wseg = __shfl_sync(0xffffffffu, rec, 4);
                 expand_produce<T>(p, ws, it, rec, stage, full, lane, 1);   // weights and y are in flight during the wait
-                if (lane == 0) {                               // v of this (projection, work segment) final?
-                    const volatile unsigned* flag = &ws.ready[(size_t)it.proj * p.cap + wseg];
+                const int key = it.proj * p.cap + wseg;
+                if (key != polled && lane == 0) {              // v of this (projection, work segment) final?
+                    const volatile unsigned* flag = &ws.ready[key];
                     unsigned i = 0;
                     while (*flag != ready_val) {
                         if (++i >= kSpinLimit || ((i & 0x3fffu) == 0 && *reinterpret_cast<volatile unsigned*>(err) != 0u)) {
@@ -833,19 +939,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                         }
                     }
                     __threadfence();
-                    asm volatile("fence.proxy.async;" ::: "memory");   // generic writes of v -> bulk-copy reads
                 }
+                polled = key;
                 __syncwarp();
+                asm volatile("fence.proxy.async;" ::: "memory");       // generic writes of v -> bulk-copy reads
                 expand_produce<T>(p, ws, it, rec, stage, full, lane, 2);
             }
-            // advance this warp's cursor by kProdWarps items and fetch the next record
-            Cursor nxt = cur;
-#pragma unroll
-            for (int q = 0; q < kProdWarps; ++q) cursor_next(p, n_units, expand, nxt);
+            // advance this warp's cursor by kProdWarps items
             const int n2 = n + kProdWarps;
-            const bool same_phase = expand ? (n2 < n_total) : (n2 < nl_a);
-            cur = nxt;
-            rec = (same_phase && lane < 16) ? __ldg(pv.unit_tab + (size_t)cur.unit * 16 + lane) : 0;
+            if (expand ? (n2 < n_total) : (n2 < nl_a)) cursor_advance(p, n_units, expand, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
     } else {
         // ---------------- consumer warps ----------------
@@ -857,6 +959,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
         Run run;
         run.proj = -1; run.wseg = -1; run.count = 0;
         run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
+        Pending pd;
+        pd.run = run; pd.old = 0u; pd.have = false;
+        unsigned bf[2][4][2];                              // v fragments of the last (projection, work segment)
+        int bf_key = -1;
         for (int n = 0; n < n_total; ++n) {
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
@@ -869,25 +975,29 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
             TLN(4)
             unsigned char* stage = smem + s * kFusedStage;
             if (kind == kKindFlush) {
-                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, ready_val);
+                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd, ready_val);
+                shrink_settle<T>(p, ws, pd, s_flag, tid, ready_val);
                 run.count = 0; run.proj = -1; run.wseg = -1;
             } else if (kind == kKindShrink) {
                 if (m.valid) {
                     if (m.proj != run.proj || m.u.wseg != run.wseg) {
-                        if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, ready_val);
+                        if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd, ready_val);
                         run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
                         run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
                     }
-                    shrink_consume<T>(m, stage, acc, tid TLC_PASS);
+                    shrink_consume_any<T>(m, stage, acc, tid TLC_PASS);
                     ++run.count;
                 }
             } else {
                 if (m.valid) {
+                    const int key = m.proj * p.cap + m.u.wseg;
+                    const bool reuse = key == bf_key;
+                    bf_key = key;
                     switch (m.u.rank) {
-                        case 8:  expand_consume<T, 8>(p, m, stage, tid TLC_PASS); break;
-                        case 16: expand_consume<T, 16>(p, m, stage, tid TLC_PASS); break;
-                        case 32: expand_consume<T, 32>(p, m, stage, tid TLC_PASS); break;
-                        default: expand_consume<T, 64>(p, m, stage, tid TLC_PASS); break;
+                        case 8:  expand_consume<T, 8>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                        case 16: expand_consume<T, 16>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                        case 32: expand_consume<T, 32>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                        default: expand_consume<T, 64>(p, m, stage, tid, bf, reuse TLC_PASS); break;
                     }
                 }
             }
