@@ -251,26 +251,44 @@ __device__ __forceinline__ long long item_row0(const ApplyParams& p, const Item&
 // =============================================================================================
 // Stage layout: weight boxes b = (row group) * ncb + (column block), each [8 rows x 128 cols]
 // contiguous (row pitch 256 B); then the x tile, one row per token, pitch KC*2 + 64 bytes.
+// `parts` bit 0: the barrier's byte count and the weight boxes (never written while kernels of
+// this library run, so they may be requested before the predecessor kernel has ended); bit 1:
+// the x rows.
 template <typename T>
 __device__ __forceinline__ void shrink_produce(const ApplyParams& p, const Item& m, int rec, unsigned stage,
-                                               unsigned bar, int lane) {
+                                               unsigned bar, int lane, int parts = 3) {
     const ProjArgs& pj = p.proj[m.proj];
     const int r = m.rank;
     const int kc_cols = kSuper / n_sub(r);                // 512, 512, 256, 128
     const int ncb = kc_cols / kBoxCols;                   // 4, 4, 2, 1
     const int nbox = ncb * (r / kBoxRows);                // 4, 8, 8, 8
     const unsigned row_bytes = m.width_ok * 2;
-    if (lane == 0) mbar_arrive_expect_tx(bar, nbox * kBoxBytes + m.ntok * row_bytes);
-    __syncwarp();
-    if (lane < nbox) {
-        const int rg = lane / ncb, cb = lane - rg * ncb;
-        tensor_g2s_2d(stage + lane * kBoxBytes, &p.amap[m.proj], m.c0 + cb * kBoxCols,
-                      (int)item_row0(p, m) + rg * kBoxRows, bar);
+    if (parts & 1) {
+        if (lane == 0) mbar_arrive_expect_tx(bar, nbox * kBoxBytes + m.ntok * row_bytes);
+        __syncwarp();
+        if (lane < nbox) {
+            const int rg = lane / ncb, cb = lane - rg * ncb;
+            tensor_g2s_2d(stage + lane * kBoxBytes, &p.amap[m.proj], m.c0 + cb * kBoxCols,
+                          (int)item_row0(p, m) + rg * kBoxRows, bar);
+        }
     }
     // lanes 8..15 hold the token rows of the unit record
-    if (lane >= 8 && lane < 8 + m.ntok)
+    if ((parts & 2) && lane >= 8 && lane < 8 + m.ntok)
         bulk_g2s(stage + kWTile + (lane - 8) * (kc_cols * 2 + kXPad),
                  reinterpret_cast<const T*>(pj.x) + (long long)rec * pj.ldx + m.c0, row_bytes, bar);
+}
+
+// An item and its record as the meta slot holds them (for the parts of a unit that are
+// requested after the rest).
+__device__ __forceinline__ Item item_of_meta(const Meta& m) {
+    Item it;
+    it.adapter = m.u.adapter; it.rank = m.u.rank; it.sub = m.u.sub; it.ntok = m.u.ntok; it.start = m.u.start;
+    it.cum = ((long long)m.u.cum_hi << 32) | (unsigned)m.u.cum_lo;
+    it.proj = m.proj; it.c0 = m.c0; it.valid = m.valid; it.kc = m.kc; it.n_chunks = m.n_chunks; it.width_ok = m.width_ok;
+    return it;
+}
+__device__ __forceinline__ int record_of_meta(const Meta& m, int lane) {
+    return lane < 16 ? reinterpret_cast<const int*>(&m)[lane] : 0;
 }
 
 // Weight rows are the M rows of the MMA (16 per block), the unit's tokens its N columns.  The 8
@@ -335,19 +353,11 @@ struct Pending {
     bool have;
 };
 
-// Looks at the arrival of a published run: the CTA whose arrival completed the (projection,
-// work segment) folds the partials in ascending k order into v and marks it ready.
+// Folds the partials of a completed (projection, work segment) in ascending k order into v and
+// marks it ready; called by all consumer threads of the CTA whose arrival completed the segment.
 template <typename T>
-__device__ __forceinline__ void shrink_settle(const ApplyParams& p, const WorkspaceView& ws, Pending& pd, int* s_flag,
-                                              int tid, unsigned ready_val) {
-    if (!pd.have) return;
-    pd.have = false;
-    const Run& run = pd.run;
-    if (tid == 0) *s_flag = (pd.old + (unsigned)run.count == (unsigned)run.n_chunks) ? 1 : 0;
-    cons_sync();
-    const int last = *s_flag;
-    cons_sync();                                           // s_flag may be rewritten by the next settle
-    if (!last) return;
+__device__ __forceinline__ void shrink_fold(const ApplyParams& p, const WorkspaceView& ws, const Run& run, int tid,
+                                            unsigned ready_val) {
     __threadfence();                                       // acquire side of the other CTAs' releasing arrivals
     const int r = run.rank;
     const int outs = run.ntok * r;
@@ -385,6 +395,19 @@ __device__ __forceinline__ void shrink_settle(const ApplyParams& p, const Worksp
     }
 }
 
+// Looks at the arrival of the published run, if any, when no other run follows it.
+template <typename T>
+__device__ __forceinline__ void shrink_settle(const ApplyParams& p, const WorkspaceView& ws, Pending& pd, int* s_flag,
+                                              int tid, unsigned ready_val) {
+    if (!pd.have) return;
+    pd.have = false;
+    if (tid == 0) *s_flag = (pd.old + (unsigned)pd.run.count == (unsigned)pd.run.n_chunks) ? 1 : 0;
+    cons_sync();
+    const int last = *s_flag;
+    cons_sync();                                           // s_flag may be rewritten by a later run
+    if (last) shrink_fold<T>(p, ws, pd.run, tid, ready_val);
+}
+
 // Ends a run: cross-warp reduction, then v itself (the CTA saw every unit of the segment) or one
 // split-K partial and the arrival.  The arrival's return value is looked at by shrink_settle
 // when the next run ends, so nobody waits for the atomic.
@@ -392,7 +415,9 @@ template <typename T>
 __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const WorkspaceView& ws, const Run& run,
                                              float (&acc)[4][4], float* red, int* s_flag, int tid, Pending& pd,
                                              unsigned ready_val = 0u) {
-    shrink_settle<T>(p, ws, pd, s_flag, tid, ready_val);
+    // the pending run's arrival is broadcast with this run's first barrier
+    const bool had = pd.have;
+    if (had && tid == 0) *s_flag = (pd.old + (unsigned)pd.run.count == (unsigned)pd.run.n_chunks) ? 1 : 0;
     const int lane = tid & 31, warp = tid >> 5;
     const int r = run.rank, rp = r + 4;
     const int mb_log = r >= 64 ? 2 : r >= 32 ? 1 : 0;
@@ -414,6 +439,7 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         base[(2 * t + 1) * rp + 8] = c[3];
     }
     cons_sync();
+    const bool fold_pending = had && *s_flag != 0;
     const int outs = run.ntok * r;
     const int rshift = 31 - __clz(r);
     const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
@@ -427,7 +453,9 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         if (whole) ws.v[o] = mid_round ? Cvt<T>::round1(s) : s;
         else ws.partial[(size_t)run.first_kc * cstride + o] = s;
     }
-    cons_sync();                                           // written by all threads, red free again
+    cons_sync();                                           // written by all threads, red and s_flag free again
+    if (fold_pending) shrink_fold<T>(p, ws, pd.run, tid, ready_val);
+    pd.have = false;
     if (tid == 0) {
         const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
         if (whole) {                                       // nothing to combine across CTAs
@@ -459,7 +487,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    pdl_wait_prior();                                      // everything below may read the predecessor's output
+    // The consumers wait for the predecessor kernel here.  The producers read only the plan and
+    // the weight pools at first, which no kernel that may still be running writes, and wait
+    // before they touch x: the first weight copies overlap the predecessor's tail.
+    if (warp < kConsWarps) pdl_wait_prior();
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -480,17 +511,31 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         if (pw >= n_local) return;
         int rec;
         Cursor cur = cursor_at(p, first + pw, n_units, false, pv.unit_tab, lane, rec);
+        bool waited = false;
+        // after the wait: the x rows of the units whose weights were requested before it
+        auto late_parts = [&](int upto) {
+            pdl_wait_prior();
+            waited = true;
+            for (int k = pw; k < upto; k += kProdWarps) {
+                const Meta& mk = meta[k % kMetaSlots];
+                if (mk.valid)
+                    shrink_produce<T>(p, item_of_meta(mk), record_of_meta(mk, lane), smem_u32(smem + (k % kStages) * kShrinkStage),
+                                      smem_u32(&bars[k % kStages]), lane, 2);
+            }
+        };
         for (int n = pw; n < n_local; n += kProdWarps) {
+            if (!waited && n >= kStages) late_parts(n);
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, false);
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 1);
             publish_meta(&meta[n % kMetaSlots], rec, it, lane);
             const unsigned full = smem_u32(&bars[s]);
-            if (it.valid) shrink_produce<T>(p, it, rec, smem_u32(smem + s * kShrinkStage), full, lane);
+            if (it.valid) shrink_produce<T>(p, it, rec, smem_u32(smem + s * kShrinkStage), full, lane, waited ? 3 : 1);
             else if (lane == 0) mbar_arrive(full);
             if (n + kProdWarps < n_local) cursor_advance(p, n_units, false, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
+        if (!waited) late_parts(n_local);
         return;
     }
 
@@ -529,11 +574,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
 // =============================================================================================
 // expand
 // =============================================================================================
-// `parts` bit 0: the barrier's byte count, the weight tile and the y rows (none of which depend
-// on the shrink half); bit 1: the rows of the intermediate v.
+// `parts` bit 0: the barrier's byte count and the weight tile (may be requested before the
+// predecessor kernel has ended); bit 1: the rows of the intermediate v; bit 2: the y rows.
 template <typename T>
 __device__ __forceinline__ void expand_produce(const ApplyParams& p, const WorkspaceView& ws, const Item& m, int rec,
-                                               unsigned stage, unsigned bar, int lane, int parts = 3) {
+                                               unsigned stage, unsigned bar, int lane, int parts = 7) {
     const ProjArgs& pj = p.proj[m.proj];
     const int r = m.rank;
     const int jc = kSuper / n_sub(r);
@@ -555,7 +600,7 @@ __device__ __forceinline__ void expand_produce(const ApplyParams& p, const Works
     } else if (lane >= 8 && lane < 8 + m.ntok) {
         dst = stage + kWTile + (lane - 8) * (jc * 2 + kYPad);
         src = reinterpret_cast<const T*>(pj.y) + (long long)tok * pj.ldy + m.c0;
-        bytes = (parts & 1) ? y_bytes : 0u;
+        bytes = (parts & 4) ? y_bytes : 0u;
     } else if (lane >= 16 && lane < 16 + m.ntok) {
         dst = stage + kWTile + kYBytes + (lane - 16) * (kVPitch * 4);
         src = ws.v + ((size_t)m.proj * p.cap + m.start + (lane - 16)) * kMaxRank;
@@ -786,7 +831,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    pdl_wait_prior();
+    if (warp < kConsWarps) pdl_wait_prior();               // the producers wait before they touch y or v
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -805,17 +850,31 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         if (pw >= n_local) return;
         int rec;
         Cursor cur = cursor_at(p, first + pw, n_units, true, pv.unit_tab, lane, rec);
+        bool waited = false;
+        // after the wait: the y and v rows of the units whose weights were requested before it
+        auto late_parts = [&](int upto) {
+            pdl_wait_prior();
+            waited = true;
+            for (int k = pw; k < upto; k += kProdWarps) {
+                const Meta& mk = meta[k % kMetaSlots];
+                if (mk.valid)
+                    expand_produce<T>(p, ws, item_of_meta(mk), record_of_meta(mk, lane), smem_u32(smem + (k % kStages) * kExpandStage),
+                                      smem_u32(&bars[k % kStages]), lane, 2 | 4);
+            }
+        };
         for (int n = pw; n < n_local; n += kProdWarps) {
+            if (!waited && n >= kStages) late_parts(n);
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, true);
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
             publish_meta(&meta[n % kMetaSlots], rec, it, lane);
             const unsigned full = smem_u32(&bars[s]);
-            if (it.valid) expand_produce<T>(p, ws, it, rec, smem_u32(smem + s * kExpandStage), full, lane);
+            if (it.valid) expand_produce<T>(p, ws, it, rec, smem_u32(smem + s * kExpandStage), full, lane, waited ? 7 : 1);
             else if (lane == 0) mbar_arrive(full);
             if (n + kProdWarps < n_local) cursor_advance(p, n_units, true, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
+        if (!waited) late_parts(n_local);
         return;
     }
 
@@ -857,6 +916,23 @@ constexpr int kFusedSmem = kStages * kFusedStage + kRedBytes + kMetaSlots * (int
 static_assert(kCtasPerSm * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
 enum { kKindShrink = 0, kKindExpand = 1, kKindFlush = 2 };
 
+// A CTA's two pieces of a list of n items: piece h lies in half h of the list.
+struct Pieces {
+    int first[2], len[2];
+    __device__ __forceinline__ int item(int k) const { return k < len[0] ? first[0] + k : first[1] + (k - len[0]); }
+};
+__device__ __forceinline__ Pieces pieces_of(int n, int n_cta, int cta) {
+    Pieces pc;
+    // a second piece costs a restart of the producers' walk and an extra run: only long lists are cut
+    const int n0 = n < 48 * n_cta ? n : ((n / 2 + 3) & ~3);
+    const int per0 = (n0 + n_cta - 1) / n_cta, per1 = (n - n0 + n_cta - 1) / n_cta;
+    pc.first[0] = cta * per0;
+    pc.len[0] = max(0, min(per0, n0 - pc.first[0]));
+    pc.first[1] = n0 + cta * per1;
+    pc.len[1] = max(0, min(per1, n - pc.first[1]));
+    return pc;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(const __grid_constant__ ApplyParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -876,7 +952,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
     }
     __syncthreads();
     TL(0, 0, gtime())
-    pdl_wait_prior();
+    if (warp < kConsWarps) pdl_wait_prior();               // the producers wait before they touch x, y or the workspace
     TL(0, 1, gtime())
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
@@ -885,26 +961,45 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
     const bool dead = hdr.error || hdr.cap != p.cap;
     const int n_units = dead ? 0 : ((p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short);
     const int n_a = n_units * p.total_super_in, n_b = n_units * p.total_super_out;
-    const int per_a = (n_a + (int)gridDim.x - 1) / (int)gridDim.x, per_b = (n_b + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int first_a = blockIdx.x * per_a, first_b = blockIdx.x * per_b;
-    const int nl_a = max(0, min(per_a, n_a - first_a)), nl_b = max(0, min(per_b, n_b - first_b));
+    // Each list is cut in two halves and a CTA takes a contiguous piece of either half, first
+    // half first.  The segments of the first half are therefore complete when the CTAs are
+    // midway through their shrink units, those of the second half when they are midway through
+    // their expand units: an expand unit rarely finds its intermediate not ready yet.
+    const Pieces pa = pieces_of(n_a, (int)gridDim.x, (int)blockIdx.x), pb = pieces_of(n_b, (int)gridDim.x, (int)blockIdx.x);
+    const int nl_a = pa.len[0] + pa.len[1], nl_b = pb.len[0] + pb.len[1];
     const int n_total = nl_a + 1 + nl_b;                   // shrink units, flush marker, expand units
     unsigned* err = &ws.ctl->error;
-    const unsigned ready_val = *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) + 1u;
+    unsigned ready_val = 0u;
+    if (warp < kConsWarps) ready_val = *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) + 1u;
 
     if (warp >= kConsWarps) {
         // ---------------- producer warps (alternate items) ----------------
         const int pw = warp - kConsWarps;
+        bool waited = false;
+        // after the wait: the x rows of the shrink units whose weights were requested before it
+        auto late_parts = [&](int upto) {
+            pdl_wait_prior();
+            waited = true;
+            ready_val = *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) + 1u;
+            for (int k = pw; k < upto; k += kProdWarps) {
+                const Meta& mk = meta[k % kMetaSlots];
+                if (mk.valid)
+                    shrink_produce<T>(p, item_of_meta(mk), record_of_meta(mk, lane), smem_u32(smem + (k % kStages) * kFusedStage),
+                                      smem_u32(&bars[k % kStages]), lane, 2);
+            }
+        };
         Cursor cur;
         cur.unit = cur.sp = cur.sub = cur.proj = cur.super = cur.ns = cur.nsub_log = 0;
         int rec = 0;
-        bool have_a = false, have_b = false;
+        bool have_cur = false, cur_expand = false;
+        int cur_idx = 0;
         int polled = -1;                                       // (projection, work segment) last seen ready
         for (int n = pw; n < n_total; n += kProdWarps) {
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             Meta* slot = &meta[n % kMetaSlots];
             const unsigned full = smem_u32(&bars[s]);
+            if (!waited && (n >= kStages || n >= nl_a)) late_parts(n);
             if (n == nl_a) {                                   // flush marker
                 mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 5);
                 if (lane == 0) { slot->valid = 0; slot->pad[0] = kKindFlush; }
@@ -913,8 +1008,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                 continue;
             }
             const bool expand = n > nl_a;
-            if (!expand && !have_a) { cur = cursor_at(p, first_a + n, n_units, false, pv.unit_tab, lane, rec); have_a = true; }
-            if (expand && !have_b) { cur = cursor_at(p, first_b + (n - nl_a - 1), n_units, true, pv.unit_tab, lane, rec); have_b = true; }
+            // list index of this item; the cursor walks on if it is kProdWarps items behind it
+            const int it_idx = expand ? pb.item(n - nl_a - 1) : pa.item(n);
+            if (have_cur && cur_expand == expand && it_idx == cur_idx + kProdWarps)
+                cursor_advance(p, n_units, expand, pv.unit_tab, lane, kProdWarps, cur, rec);
+            else
+                cur = cursor_at(p, it_idx, n_units, expand, pv.unit_tab, lane, rec);
+            have_cur = true; cur_expand = expand; cur_idx = it_idx;
             const Item it = make_item(p, rec, cur, expand);
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, expand ? 3 : 1);
             publish_meta(slot, rec, it, lane);
@@ -924,10 +1024,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
             if (!it.valid) {
                 if (lane == 0) mbar_arrive(full);
             } else if (!expand) {
-                shrink_produce<T>(p, it, rec, stage, full, lane);
+                shrink_produce<T>(p, it, rec, stage, full, lane, waited ? 3 : 1);
             } else {
                 const int wseg = __shfl_sync(0xffffffffu, rec, 4);
-                expand_produce<T>(p, ws, it, rec, stage, full, lane, 1);   // weights and y are in flight during the wait
+                expand_produce<T>(p, ws, it, rec, stage, full, lane, 1 | 4);   // weights and y are in flight during the wait
                 const int key = it.proj * p.cap + wseg;
                 if (key != polled && lane == 0) {              // v of this (projection, work segment) final?
                     const volatile unsigned* flag = &ws.ready[key];
@@ -945,10 +1045,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(co
                 asm volatile("fence.proxy.async;" ::: "memory");       // generic writes of v -> bulk-copy reads
                 expand_produce<T>(p, ws, it, rec, stage, full, lane, 2);
             }
-            // advance this warp's cursor by kProdWarps items
-            const int n2 = n + kProdWarps;
-            if (expand ? (n2 < n_total) : (n2 < nl_a)) cursor_advance(p, n_units, expand, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
+        if (!waited) late_parts(min(n_total, nl_a));
     } else {
         // ---------------- consumer warps ----------------
         float acc[4][4];

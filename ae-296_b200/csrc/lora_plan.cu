@@ -227,7 +227,8 @@ template <typename IdT>
 __global__ void __launch_bounds__(kPlanThreads, 1)
 plan_build_kernel(void* plan, int cap, const void* ids, int T, const PlanAdapters ad) {
     const int N = ad.n_adapters;
-    pdl_launch_dependents();
+    // no early launch of the successor here: the apply kernels read the plan before they wait
+    // for their predecessor, which is safe only because a plan kernel has ended by then
     pdl_wait_prior();
     __shared__ int smem[64];
     PlanView pv = plan_view(plan, cap, N);
@@ -246,7 +247,8 @@ __global__ void __launch_bounds__(kPlanThreads, 1)
 plan_segments_kernel(void* plan, int cap, const int* seg_starts, const int* seg_adapter, int S, int T,
                      const PlanAdapters ad) {
     const int N = ad.n_adapters;
-    pdl_launch_dependents();
+    // no early launch of the successor here: the apply kernels read the plan before they wait
+    // for their predecessor, which is safe only because a plan kernel has ended by then
     pdl_wait_prior();
     __shared__ int smem[64];
     PlanView pv = plan_view(plan, cap, N);
