@@ -98,6 +98,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned byt
     asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
     unsigned ok;
     asm volatile(
@@ -336,88 +339,16 @@ struct Run {
     int proj, wseg, start, ntok, rank, first_kc, count, n_chunks;
 };
 
-// release only: an acquiring atomic would hold back the thread's later loads until it returns
-__device__ __forceinline__ unsigned atom_add_release(unsigned* p, unsigned v) {
-    unsigned old;
-    asm volatile("atom.add.release.gpu.global.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-    return old;
-}
-__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// A published run whose arrival count has not been looked at yet (thread 0 holds `old`).
-struct Pending {
-    Run run;
-    unsigned old;
-    bool have;
-};
-
-// Folds the partials of a completed (projection, work segment) in ascending k order into v and
-// marks it ready; called by all consumer threads of the CTA whose arrival completed the segment.
-template <typename T>
-__device__ __forceinline__ void shrink_fold(const ApplyParams& p, const WorkspaceView& ws, const Run& run, int tid,
-                                            unsigned ready_val) {
-    __threadfence();                                       // acquire side of the other CTAs' releasing arrivals
-    const int r = run.rank;
-    const int outs = run.ntok * r;
-    const int rshift = 31 - __clz(r);
-    const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
-    const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
-    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
-    const unsigned long long mask = *reinterpret_cast<volatile unsigned long long*>(&ws.masks[cidx]);
-    for (int idx = tid; idx < outs; idx += kConsThreads) {
-        const int pos = run.start + (idx >> rshift), i = idx & (r - 1);
-        const float* src = &ws.partial[((size_t)run.proj * p.cap + pos) * kMaxRank + i];
-        float s = 0.f;
-        unsigned long long mm = mask;
-        while (mm) {
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {                  // up to four loads in flight, summed in order
-                if (mm) {
-                    const int kc = __ffsll((long long)mm) - 1;
-                    mm &= mm - 1;
-                    v[j] = __ldcg(src + (size_t)kc * cstride);
-                }
-            }
-            s = (((s + v[0]) + v[1]) + v[2]) + v[3];
-        }
-        if (mid_round) s = Cvt<T>::round1(s);
-        ws.v[((size_t)run.proj * p.cap + pos) * kMaxRank + i] = s;
-    }
-    cons_sync();                                           // v written by all threads
-    if (tid == 0) {
-        ws.counters[cidx] = 0u;
-        ws.masks[cidx] = 0ull;
-        if (ready_val) st_release(&ws.ready[cidx], ready_val);     // v is final: let the expand units go
-        else __threadfence();
-    }
-}
-
-// Looks at the arrival of the published run, if any, when no other run follows it.
-template <typename T>
-__device__ __forceinline__ void shrink_settle(const ApplyParams& p, const WorkspaceView& ws, Pending& pd, int* s_flag,
-                                              int tid, unsigned ready_val) {
-    if (!pd.have) return;
-    pd.have = false;
-    if (tid == 0) *s_flag = (pd.old + (unsigned)pd.run.count == (unsigned)pd.run.n_chunks) ? 1 : 0;
-    cons_sync();
-    const int last = *s_flag;
-    cons_sync();                                           // s_flag may be rewritten by a later run
-    if (last) shrink_fold<T>(p, ws, pd.run, tid, ready_val);
-}
-
-// Ends a run: cross-warp reduction, then v itself (the CTA saw every unit of the segment) or one
-// split-K partial and the arrival.  The arrival's return value is looked at by shrink_settle
-// when the next run ends, so nobody waits for the atomic.
+// Ends a run: cross-warp reduction and one split-K partial in slot `first_kc` of the workspace.
+// Nothing else: which slots a (projection, work segment) has follows from the CTAs' item ranges,
+// so whoever needs the intermediate adds the slots up after this kernel has ended (the expand
+// kernel's producers, or fold_partials_kernel for tensor-parallel callers).  No atomics, no
+// fences; the reduction tile alternates between two buffers, so one barrier per run suffices.
 template <typename T>
 __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const WorkspaceView& ws, const Run& run,
-                                             float (&acc)[4][4], float* red, int* s_flag, int tid, Pending& pd,
-                                             unsigned ready_val = 0u) {
-    // the pending run's arrival is broadcast with this run's first barrier
-    const bool had = pd.have;
-    if (had && tid == 0) *s_flag = (pd.old + (unsigned)pd.run.count == (unsigned)pd.run.n_chunks) ? 1 : 0;
+                                             float (&acc)[4][4], float* red2, int& red_sel, int tid) {
+    float* red = red2 + red_sel * (kRedBytes / 4);
+    red_sel ^= 1;
     const int lane = tid & 31, warp = tid >> 5;
     const int r = run.rank, rp = r + 4;
     const int mb_log = r >= 64 ? 2 : r >= 32 ? 1 : 0;
@@ -439,43 +370,76 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         base[(2 * t + 1) * rp + 8] = c[3];
     }
     cons_sync();
-    const bool fold_pending = had && *s_flag != 0;
     const int outs = run.ntok * r;
     const int rshift = 31 - __clz(r);
     const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
-    const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
-    const bool whole = run.count == run.n_chunks;          // this CTA saw every unit of the segment
+    float* dst = ws.partial + (size_t)run.first_kc * cstride + ((size_t)run.proj * p.cap + run.start) * kMaxRank;
     for (int idx = tid; idx < outs; idx += kConsThreads) {
         const int tok = idx >> rshift, i = idx & (r - 1);
         float s = 0.f;
         for (int w = 0; w < ksplit; ++w) s += red[(w * 8 + tok) * rp + i];
-        const size_t o = ((size_t)run.proj * p.cap + run.start + tok) * kMaxRank + i;
-        if (whole) ws.v[o] = mid_round ? Cvt<T>::round1(s) : s;
-        else ws.partial[(size_t)run.first_kc * cstride + o] = s;
+        dst[tok * kMaxRank + i] = s;
     }
-    cons_sync();                                           // written by all threads, red and s_flag free again
-    if (fold_pending) shrink_fold<T>(p, ws, pd.run, tid, ready_val);
-    pd.have = false;
-    if (tid == 0) {
-        const size_t cidx = (size_t)run.proj * p.cap + run.wseg;
-        if (whole) {                                       // nothing to combine across CTAs
-            if (ready_val) st_release(&ws.ready[cidx], ready_val);
-            else __threadfence();
-        } else {
-            atomicOr(&ws.masks[cidx], 1ull << run.first_kc);   // no return value: a reduction, not waited for
-            pd.old = atom_add_release(&ws.counters[cidx], (unsigned)run.count);
+}
+
+// The split-K slots of one (projection, work segment): the runs of the shrink kernel start at
+// the segment's first unit and wherever a CTA's item range starts inside the segment, and a
+// run's slot is the index, inside the segment, of its first unit.  `seg_first` is the list
+// index of the segment's first unit, `per_cta` the length of a CTA's range, `n_chunks` the
+// units of the segment that lie inside the matrix (they come first).
+struct SlotWalk {
+    int j, step, n_chunks;
+    __device__ __forceinline__ SlotWalk(int seg_first, int per_cta, int n_chunks_) : j(0), n_chunks(n_chunks_) {
+        step = per_cta - seg_first % per_cta;              // distance to the next range start
+    }
+    __device__ __forceinline__ bool valid() const { return j < n_chunks; }
+    __device__ __forceinline__ void next(int per_cta) { j += step; step = per_cta; }
+};
+// list index of the first shrink unit of the segment that starts at plan unit `u0`
+__device__ __forceinline__ int shrink_seg_first(const ApplyParams& p, int n_units, int proj, int u0) {
+    int base = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxProj - 1; ++i)
+        if (i < proj) base += n_units * p.proj[i].n_super_in;
+    return base + u0 * p.proj[proj].n_super_in;
+}
+__device__ __forceinline__ int shrink_chunks(const ApplyParams& p, int proj, int rank) {
+    const int wshift = rank <= 16 ? 9 : rank == 32 ? 8 : 7;
+    return (p.proj[proj].h_in + (1 << wshift) - 1) >> wshift;
+}
+
+// Adds up the slots of one segment for four consecutive rank indices of one token, ascending.
+template <typename T>
+__device__ __forceinline__ float4 fold_quad(const ApplyParams& p, const WorkspaceView& ws, size_t off, int seg_first,
+                                            int per_cta, int n_chunks) {
+    const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    SlotWalk sw(seg_first, per_cta, n_chunks);
+    while (sw.valid()) {
+        float4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {                      // up to four loads in flight, summed in order
+            v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (sw.valid()) {
+                v[q] = __ldcg(reinterpret_cast<const float4*>(ws.partial + (size_t)sw.j * cstride + off));
+                sw.next(per_cta);
+            }
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { s.x += v[q].x; s.y += v[q].y; s.z += v[q].z; s.w += v[q].w; }
     }
-    if (!whole) { pd.run = run; pd.have = true; }
+    if (p.flags & B200_LORA_MID_ROUND) {
+        s.x = Cvt<T>::round1(s.x); s.y = Cvt<T>::round1(s.y); s.z = Cvt<T>::round1(s.z); s.w = Cvt<T>::round1(s.w);
+    }
+    return s;
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(const __grid_constant__ ApplyParams p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    float* red = reinterpret_cast<float*>(smem + kStages * kShrinkStage);
-    Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kShrinkStage + kRedBytes);
+    float* red2 = reinterpret_cast<float*>(smem + kStages * kShrinkStage);      // two reduction tiles
+    Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kShrinkStage + 2 * kRedBytes);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
-    int* s_flag = reinterpret_cast<int*>(bars + 2 * kStages);
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -548,8 +512,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     Run run;
     run.proj = -1; run.wseg = -1; run.count = 0;
     run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
-    Pending pd;
-    pd.run = run; pd.old = 0u; pd.have = false;
+    int red_sel = 0;
     for (int n = 0; n < n_local; ++n) {
         const int s = n % kStages;
         const unsigned ph = (n / kStages) & 1;
@@ -557,7 +520,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         const Meta& m = meta[n % kMetaSlots];
         if (m.valid) {
             if (m.proj != run.proj || m.u.wseg != run.wseg) {
-                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd);
+                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red2, red_sel, tid);
                 run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
                 run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
             }
@@ -567,26 +530,39 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));      // this warp is done with the stage
     }
-    if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd);
-    shrink_settle<T>(p, ws, pd, s_flag, tid, 0u);
+    if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red2, red_sel, tid);
 }
 
 // =============================================================================================
 // expand
 // =============================================================================================
-// `parts` bit 0: the barrier's byte count and the weight tile (may be requested before the
-// predecessor kernel has ended); bit 1: the rows of the intermediate v; bit 2: the y rows.
+// What the expand producers need to add up a segment's split-K slots themselves.
+struct FoldCtx {
+    int n_units;      // units of the plan (0: the intermediate is final in the workspace already)
+    int per_cta;      // length of a CTA's item range in the shrink kernel
+};
+
+// `parts` bit 0: the barrier's byte count and the weight tile (never written while kernels of
+// this library run, so they may be requested before the predecessor kernel has ended); bit 2:
+// the y rows; bit 1, always last: the intermediate v and the producer's arrival.  v is needed
+// only by the first unit a CTA has of a (projection, work segment) - the consumers keep its
+// fragments for the units that follow - and comes either from the workspace (a tensor-parallel
+// caller has summed it over the ranks) or from the shrink kernel's split-K slots, which the
+// producer warp adds up in ascending k order straight into the stage.
 template <typename T>
 __device__ __forceinline__ void expand_produce(const ApplyParams& p, const WorkspaceView& ws, const Item& m, int rec,
-                                               unsigned stage, unsigned bar, int lane, int parts = 7) {
+                                               unsigned char* stage_ptr, unsigned bar, int lane, int parts, bool need_v,
+                                               const FoldCtx& fc, int u0) {
+    const unsigned stage = smem_u32(stage_ptr);
     const ProjArgs& pj = p.proj[m.proj];
     const int r = m.rank;
     const int jc = kSuper / n_sub(r);
     const unsigned w_bytes = m.width_ok * r * 2;
     const unsigned y_bytes = (p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD)) ? 0u : m.width_ok * 2;
-    const unsigned v_bytes = r * 4;
+    const bool v_copy = need_v && fc.n_units == 0;
+    const unsigned v_bytes = v_copy ? r * 4 : 0u;
     if (parts & 1) {
-        if (lane == 0) mbar_arrive_expect_tx(bar, w_bytes + m.ntok * (y_bytes + v_bytes));
+        if (lane == 0) mbar_expect_tx(bar, w_bytes + m.ntok * (y_bytes + v_bytes));
         __syncwarp();
     }
     // one instruction: lane 0 the weight tile, lanes 8..15 the y rows, lanes 16..23 the v rows
@@ -607,6 +583,21 @@ __device__ __forceinline__ void expand_produce(const ApplyParams& p, const Works
         bytes = (parts & 2) ? v_bytes : 0u;
     }
     if (bytes) bulk_g2s(dst, src, bytes, bar);
+    if (parts & 2) {
+        if (need_v && !v_copy) {
+            float* vt = reinterpret_cast<float*>(stage_ptr + kWTile + kYBytes);
+            const int seg_first = shrink_seg_first(p, fc.n_units, m.proj, u0);
+            const int n_chunks = shrink_chunks(p, m.proj, r);
+            const int qshift = 31 - __clz(r >> 2);             // quads of four rank indices per token
+            for (int idx = lane; idx < ((m.ntok * r) >> 2); idx += 32) {
+                const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
+                const size_t off = ((size_t)m.proj * p.cap + m.start + t) * kMaxRank + k4;
+                *reinterpret_cast<float4*>(vt + t * kVPitch + k4) = fold_quad<T>(p, ws, off, seg_first, fc.per_cta, n_chunks);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);                       // releases the v tile with it
+    }
 }
 
 // One packed 16-bit pair of the hi halves (the values rounded to T) or of the lo halves (what
@@ -850,16 +841,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         if (pw >= n_local) return;
         int rec;
         Cursor cur = cursor_at(p, first + pw, n_units, true, pv.unit_tab, lane, rec);
+        FoldCtx fc;
+        fc.n_units = (p.flags & B200_LORA_ONLY_EXPAND) ? 0 : n_units;
+        fc.per_cta = (n_units * p.total_super_in + (int)gridDim.x - 1) / (int)gridDim.x;
         bool waited = false;
-        // after the wait: the y and v rows of the units whose weights were requested before it
+        // after the wait: y and v of the units whose weights were requested before it; the meta
+        // slot's spare words hold what that takes (first unit of the segment, does it need v)
         auto late_parts = [&](int upto) {
             pdl_wait_prior();
             waited = true;
             for (int k = pw; k < upto; k += kProdWarps) {
                 const Meta& mk = meta[k % kMetaSlots];
                 if (mk.valid)
-                    expand_produce<T>(p, ws, item_of_meta(mk), record_of_meta(mk, lane), smem_u32(smem + (k % kStages) * kExpandStage),
-                                      smem_u32(&bars[k % kStages]), lane, 2 | 4);
+                    expand_produce<T>(p, ws, item_of_meta(mk), record_of_meta(mk, lane), smem + (k % kStages) * kExpandStage,
+                                      smem_u32(&bars[k % kStages]), lane, 2 | 4, mk.pad[0] != 0, fc, mk.pad[1]);
             }
         };
         for (int n = pw; n < n_local; n += kProdWarps) {
@@ -867,10 +862,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, true);
+            // the CTA's first unit of a (projection, work segment) brings the intermediate along
+            const bool need_v = n == 0 || (cur.sp == 0 && cur.sub == 0);
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
-            publish_meta(&meta[n % kMetaSlots], rec, it, lane);
+            Meta* slot = &meta[n % kMetaSlots];
+            publish_meta(slot, rec, it, lane);
+            if (lane == 0) { slot->pad[0] = need_v ? 1 : 0; slot->pad[1] = cur.unit; }
+            __syncwarp();
             const unsigned full = smem_u32(&bars[s]);
-            if (it.valid) expand_produce<T>(p, ws, it, rec, smem_u32(smem + s * kExpandStage), full, lane, waited ? 7 : 1);
+            if (it.valid) expand_produce<T>(p, ws, it, rec, smem + s * kExpandStage, full, lane, waited ? 7 : 1, need_v, fc, cur.unit);
             else if (lane == 0) mbar_arrive(full);
             if (n + kProdWarps < n_local) cursor_advance(p, n_units, true, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
@@ -902,227 +902,43 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
     }
 }
 
-// =============================================================================================
-// fused shrink -> expand
-// =============================================================================================
-// One launch per apply: every CTA first streams its range of shrink units, then a marker that
-// makes its consumers publish whatever run they still hold, then its range of expand units.
-// Before loading an expand unit the producer waits (bounded) until the unit's (projection, work
-// segment) has been marked ready by whichever CTA finished its v; ready words hold the launch
-// epoch + 1, so they never need clearing.  Shrink work never waits on anything, so the CTAs
-// make progress in any order as long as the grid is resident (it is sized to 2 CTAs per SM).
-constexpr int kFusedStage = kShrinkStage > kExpandStage ? kShrinkStage : kExpandStage;
-constexpr int kFusedSmem = kStages * kFusedStage + kRedBytes + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
-static_assert(kCtasPerSm * (kFusedSmem + 1024) <= 233472, "two CTAs must fit one SM");
-enum { kKindShrink = 0, kKindExpand = 1, kKindFlush = 2 };
-
-// A CTA's two pieces of a list of n items: piece h lies in half h of the list.
-struct Pieces {
-    int first[2], len[2];
-    __device__ __forceinline__ int item(int k) const { return k < len[0] ? first[0] + k : first[1] + (k - len[0]); }
-};
-__device__ __forceinline__ Pieces pieces_of(int n, int n_cta, int cta) {
-    Pieces pc;
-    // a second piece costs a restart of the producers' walk and an extra run: only long lists are cut
-    const int n0 = n < 48 * n_cta ? n : ((n / 2 + 3) & ~3);
-    const int per0 = (n0 + n_cta - 1) / n_cta, per1 = (n - n0 + n_cta - 1) / n_cta;
-    pc.first[0] = cta * per0;
-    pc.len[0] = max(0, min(per0, n0 - pc.first[0]));
-    pc.first[1] = n0 + cta * per1;
-    pc.len[1] = max(0, min(per1, n - pc.first[1]));
-    return pc;
-}
-
+// For tensor-parallel callers, who sum the intermediate over the ranks between the two halves:
+// adds up the split-K slots of every (projection, work segment) into v in the workspace.
 template <typename T>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_fused_tma_kernel(const __grid_constant__ ApplyParams p) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    float* red = reinterpret_cast<float*>(smem + kStages * kFusedStage);
-    Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kFusedStage + kRedBytes);
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
-    int* s_flag = reinterpret_cast<int*>(bars + 2 * kStages);
-
+__global__ void __launch_bounds__(128) fold_partials_kernel(const __grid_constant__ ApplyParams p, int shrink_grid) {
     pdl_launch_dependents();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[kStages + s]), kConsWarps);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    TL(0, 0, gtime())
-    if (warp < kConsWarps) pdl_wait_prior();               // the producers wait before they touch x, y or the workspace
-    TL(0, 1, gtime())
-
+    pdl_wait_prior();
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
-    const bool dead = hdr.error || hdr.cap != p.cap;
-    const int n_units = dead ? 0 : ((p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short);
-    const int n_a = n_units * p.total_super_in, n_b = n_units * p.total_super_out;
-    // Each list is cut in two halves and a CTA takes a contiguous piece of either half, first
-    // half first.  The segments of the first half are therefore complete when the CTAs are
-    // midway through their shrink units, those of the second half when they are midway through
-    // their expand units: an expand unit rarely finds its intermediate not ready yet.
-    const Pieces pa = pieces_of(n_a, (int)gridDim.x, (int)blockIdx.x), pb = pieces_of(n_b, (int)gridDim.x, (int)blockIdx.x);
-    const int nl_a = pa.len[0] + pa.len[1], nl_b = pb.len[0] + pb.len[1];
-    const int n_total = nl_a + 1 + nl_b;                   // shrink units, flush marker, expand units
-    unsigned* err = &ws.ctl->error;
-    unsigned ready_val = 0u;
-    if (warp < kConsWarps) ready_val = *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) + 1u;
-
-    if (warp >= kConsWarps) {
-        // ---------------- producer warps (alternate items) ----------------
-        const int pw = warp - kConsWarps;
-        bool waited = false;
-        // after the wait: the x rows of the shrink units whose weights were requested before it
-        auto late_parts = [&](int upto) {
-            pdl_wait_prior();
-            waited = true;
-            ready_val = *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) + 1u;
-            for (int k = pw; k < upto; k += kProdWarps) {
-                const Meta& mk = meta[k % kMetaSlots];
-                if (mk.valid)
-                    shrink_produce<T>(p, item_of_meta(mk), record_of_meta(mk, lane), smem_u32(smem + (k % kStages) * kFusedStage),
-                                      smem_u32(&bars[k % kStages]), lane, 2);
-            }
-        };
-        Cursor cur;
-        cur.unit = cur.sp = cur.sub = cur.proj = cur.super = cur.ns = cur.nsub_log = 0;
-        int rec = 0;
-        bool have_cur = false, cur_expand = false;
-        int cur_idx = 0;
-        int polled = -1;                                       // (projection, work segment) last seen ready
-        for (int n = pw; n < n_total; n += kProdWarps) {
-            const int s = n % kStages;
-            const unsigned ph = (n / kStages) & 1;
-            Meta* slot = &meta[n % kMetaSlots];
-            const unsigned full = smem_u32(&bars[s]);
-            if (!waited && (n >= kStages || n >= nl_a)) late_parts(n);
-            if (n == nl_a) {                                   // flush marker
-                mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 5);
-                if (lane == 0) { slot->valid = 0; slot->pad[0] = kKindFlush; }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full);
-                continue;
-            }
-            const bool expand = n > nl_a;
-            // list index of this item; the cursor walks on if it is kProdWarps items behind it
-            const int it_idx = expand ? pb.item(n - nl_a - 1) : pa.item(n);
-            if (have_cur && cur_expand == expand && it_idx == cur_idx + kProdWarps)
-                cursor_advance(p, n_units, expand, pv.unit_tab, lane, kProdWarps, cur, rec);
-            else
-                cur = cursor_at(p, it_idx, n_units, expand, pv.unit_tab, lane, rec);
-            have_cur = true; cur_expand = expand; cur_idx = it_idx;
-            const Item it = make_item(p, rec, cur, expand);
-            mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, expand ? 3 : 1);
-            publish_meta(slot, rec, it, lane);
-            if (lane == 0) slot->pad[0] = expand ? kKindExpand : kKindShrink;
-            __syncwarp();
-            const unsigned stage = smem_u32(smem + s * kFusedStage);
-            if (!it.valid) {
-                if (lane == 0) mbar_arrive(full);
-            } else if (!expand) {
-                shrink_produce<T>(p, it, rec, stage, full, lane, waited ? 3 : 1);
-            } else {
-                const int wseg = __shfl_sync(0xffffffffu, rec, 4);
-                expand_produce<T>(p, ws, it, rec, stage, full, lane, 1 | 4);   // weights and y are in flight during the wait
-                const int key = it.proj * p.cap + wseg;
-                if (key != polled && lane == 0) {              // v of this (projection, work segment) final?
-                    const volatile unsigned* flag = &ws.ready[key];
-                    unsigned i = 0;
-                    while (*flag != ready_val) {
-                        if (++i >= kSpinLimit || ((i & 0x3fffu) == 0 && *reinterpret_cast<volatile unsigned*>(err) != 0u)) {
-                            atomicMax(err, 6u);
-                            break;
-                        }
-                    }
-                    __threadfence();
-                }
-                polled = key;
-                __syncwarp();
-                asm volatile("fence.proxy.async;" ::: "memory");       // generic writes of v -> bulk-copy reads
-                expand_produce<T>(p, ws, it, rec, stage, full, lane, 2);
-            }
-        }
-        if (!waited) late_parts(min(n_total, nl_a));
-    } else {
-        // ---------------- consumer warps ----------------
-        float acc[4][4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-        Run run;
-        run.proj = -1; run.wseg = -1; run.count = 0;
-        run.start = run.ntok = run.rank = run.first_kc = run.n_chunks = 0;
-        Pending pd;
-        pd.run = run; pd.old = 0u; pd.have = false;
-        unsigned bf[2][4][2];                              // v fragments of the last (projection, work segment)
-        int bf_key = -1;
-        for (int n = 0; n < n_total; ++n) {
-            const int s = n % kStages;
-            const unsigned ph = (n / kStages) & 1;
-            TL(n + 1, 0, gtime())
-            mbar_wait(smem_u32(&bars[s]), ph, err, 2);
-            TL(n + 1, 1, gtime())
-            const Meta& m = meta[n % kMetaSlots];
-            const int kind = m.pad[0];
-            TL(n + 1, 3, (unsigned long long)(kind | (m.u.rank << 8) | (m.u.ntok << 16) | (m.valid << 24)))
-            TLN(4)
-            unsigned char* stage = smem + s * kFusedStage;
-            if (kind == kKindFlush) {
-                if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd, ready_val);
-                shrink_settle<T>(p, ws, pd, s_flag, tid, ready_val);
-                run.count = 0; run.proj = -1; run.wseg = -1;
-            } else if (kind == kKindShrink) {
-                if (m.valid) {
-                    if (m.proj != run.proj || m.u.wseg != run.wseg) {
-                        if (run.count > 0) shrink_flush<T>(p, ws, run, acc, red, s_flag, tid, pd, ready_val);
-                        run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
-                        run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
-                    }
-                    shrink_consume_any<T>(m, stage, acc, tid TLC_PASS);
-                    ++run.count;
-                }
-            } else {
-                if (m.valid) {
-                    const int key = m.proj * p.cap + m.u.wseg;
-                    const bool reuse = key == bf_key;
-                    bf_key = key;
-                    switch (m.u.rank) {
-                        case 8:  expand_consume<T, 8>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                        case 16: expand_consume<T, 16>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                        case 32: expand_consume<T, 32>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                        default: expand_consume<T, 64>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));
-            TLN(10)
-            TL(n + 1, 2, gtime())
-        }
-    }
-    __syncthreads();
-    TL(0, 2, gtime())
-    TL(0, 3, (unsigned long long)n_total)
-    if (tid == 0) {                                            // the last CTA out advances the epoch
-        __threadfence();
-        const unsigned d = atomicAdd(&ws.ctl->done[0], 1u);
-        if (d == gridDim.x - 1) {
-            ws.ctl->done[0] = 0u;
-            *reinterpret_cast<volatile unsigned*>(&ws.ctl->epoch) = ready_val;
+    if (hdr.error || hdr.cap != p.cap) return;
+    const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
+    const int per_cta = (n_units * p.total_super_in + shrink_grid - 1) / shrink_grid;
+    const int proj = blockIdx.y;
+    // the units with sub-range 0 are the first units of the work segments
+    for (int u0 = blockIdx.x; u0 < n_units; u0 += gridDim.x) {
+        const UnitRec* rec = reinterpret_cast<const UnitRec*>(pv.unit_tab) + u0;
+        if (rec->sub != 0) continue;
+        const int r = rec->rank, ntok = rec->ntok, start = rec->start;
+        const int seg_first = shrink_seg_first(p, n_units, proj, u0);
+        const int n_chunks = shrink_chunks(p, proj, r);
+        const int qshift = 31 - __clz(r >> 2);
+        for (int idx = threadIdx.x; idx < ((ntok * r) >> 2); idx += blockDim.x) {
+            const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
+            const size_t off = ((size_t)proj * p.cap + start + t) * kMaxRank + k4;
+            *reinterpret_cast<float4*>(ws.v + off) = fold_quad<T>(p, ws, off, seg_first, per_cta, n_chunks);
         }
     }
 }
 
-constexpr int kShrinkSmem = kStages * kShrinkStage + kRedBytes + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
+constexpr int kShrinkSmem = kStages * kShrinkStage + 2 * kRedBytes + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
 constexpr int kExpandSmem = kStages * kExpandStage + kMetaSlots * (int)sizeof(Meta) + 2 * kStages * 8 + 16;
 static_assert(kCtasPerSm * (kShrinkSmem + 1024) <= 233472 && kCtasPerSm * (kExpandSmem + 1024) <= 233472,
               "two CTAs must fit the 228 KB of shared memory of one SM");
 
+// shrink kernel, then expand kernel (whose producers add up the split-K slots), each launched so
+// that its prologue and first weight copies overlap its predecessor's tail; callers that want
+// only one half get that half, and after a lone shrink half the intermediate is written out.
 template <typename T>
 cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
     static bool configured[64] = {false};
@@ -1133,15 +949,15 @@ cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
         if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(bgmv_expand_tma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpandSmem);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(bgmv_fused_tma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFusedSmem);
-        if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int grid = n_sm * kCtasPerSm;
-    if (!(p.flags & (B200_LORA_ONLY_EXPAND | B200_LORA_ONLY_SHRINK | B200_LORA_TWO_KERNELS)))
-        return launch_pdl(bgmv_fused_tma_kernel<T>, grid, kThreads, kFusedSmem, s, p);
     cudaError_t e = cudaSuccess;
-    if (!(p.flags & B200_LORA_ONLY_EXPAND)) e = launch_pdl(bgmv_shrink_tma_kernel<T>, grid, kThreads, kShrinkSmem, s, p);
+    if (!(p.flags & B200_LORA_ONLY_EXPAND)) {
+        e = launch_pdl(bgmv_shrink_tma_kernel<T>, grid, kThreads, kShrinkSmem, s, p);
+        if (e == cudaSuccess && (p.flags & B200_LORA_ONLY_SHRINK))
+            e = launch_pdl(fold_partials_kernel<T>, dim3(n_sm, p.n_proj), 128, 0, s, p, grid);
+    }
     if (e == cudaSuccess && !(p.flags & B200_LORA_ONLY_SHRINK))
         e = launch_pdl(bgmv_expand_tma_kernel<T>, grid, kThreads, kExpandSmem, s, p);
     return e;
