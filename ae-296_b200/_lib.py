@@ -12,7 +12,7 @@ import os
 from .build import LIB_PATH
 
 F16, BF16, F32 = 0, 1, 2
-MID_ROUND, NO_TENSOR, ONLY_SHRINK, ONLY_EXPAND, TWO_KERNELS, DELTA_THEN_ADD = 1, 2, 4, 8, 16, 32
+MID_ROUND, NO_TENSOR, ONLY_SHRINK, ONLY_EXPAND, DELTA_THEN_ADD = 1, 2, 4, 8, 32
 MAX_RANK, MAX_PROJ = 64, 4
 
 STATUS = {

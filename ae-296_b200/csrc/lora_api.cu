@@ -364,12 +364,10 @@ int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, cons
     }
     void* scratch = dev_ptr[dev];
     // The array keeps whatever the previous call left.  The kernels need their control words
-    // (tickets, arrival counters, slot masks, error word) to start at zero: clear that prefix
-    // of the workspace part; the plan part is rebuilt from scratch by every call.
+    // (arrival counters, error word) to start at zero: clear that prefix of the workspace part;
+    // the plan part is rebuilt from scratch by every call.
     const size_t pb = (b200_lora_plan_bytes(n_tokens, n_adapters) + 255) & ~size_t(255);
-    const size_t ctl_bytes = sizeof(WorkspaceCtl) + 8 * ((ws_counter_words(n_tokens) + 3) & ~size_t(3)) +
-                             8 * ws_counter_words(n_tokens);
-    e = cudaMemsetAsync(static_cast<char*>(scratch) + pb, 0, ctl_bytes, static_cast<cudaStream_t>(stream));
+    e = cudaMemsetAsync(static_cast<char*>(scratch) + pb, 0, ws_ctl_bytes(n_tokens), static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e);
     return b200_add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, indicies_are_i64, n_tokens, h_in, h_out,
                               n_adapters, n_layers, r, layer_idx, scale, dtype, scratch,

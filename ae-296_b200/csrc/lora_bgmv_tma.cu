@@ -1,29 +1,38 @@
-// Decode BGMV, fast path: TMA copies + mbarrier pipeline + mma.sync.
+// Decode BGMV, fast path: TMA copies + mbarrier pipeline + mma.sync (sm_100a).
 //
 // Used when every adapter rank is 8, 16, 32 or 64 and every projection width is a multiple of
-// 256.  A CTA is two producer warps plus eight consumer warps around a 4-stage shared-memory
-// ring; two CTAs share an SM, so ~100 KB of loads per SM are in flight.  The producers walk a
-// contiguous range of <= 16 KB weight units (alternate units each) and fill a stage with ONE instruction per kind:
+// 256.  One apply is two launches, a shrink kernel (v = x . A^T per work segment) and an expand
+// kernel (y += scale * v . B^T); both are lists of <= 16 KB weight units, ordered projection by
+// projection and work segment by work segment, of which every CTA takes a contiguous range.
+// A CTA is two producer warps plus eight consumer warps around a 4-stage shared-memory ring;
+// two CTAs share an SM, so ~100 KB of loads per SM are in flight.  The producers walk the range
+// (alternate units each) and fill a stage with ONE instruction per kind:
 //   shrink  A rows [r, KC]   -> up to eight [8 x 128] boxes of a 2-D tensor map over the A pool
 //           x rows [ntok, KC]-> one bulk copy per token
 //   expand  B rows [JC, r]   -> one contiguous bulk copy; plus one copy per token for the y
-//           tile that will be updated and for the fp32 intermediate
+//           tile that will be updated
 // Each stage's arrival is tracked by an mbarrier transaction count; consumers never compute a
-// load address.  They read MMA fragments with 128-bit shared loads (tiles are stored
-// unswizzled; the k index inside a 32-wide block is permuted identically for both operands so
-// that a thread's fragment is one contiguous 16-byte chunk) and run mma.sync m16n8k16 with
-// fp32 accumulators.  The legacy MMA path of this part has a long dependent-issue latency, so
-// every warp keeps several independent accumulators in flight.
+// load address.  They read MMA fragments with wide shared loads (tiles are stored unswizzled;
+// the k index is permuted identically for both operands so that a thread's fragment is one
+// contiguous chunk) and run mma.sync m16n8k16 with fp32 accumulators.  The legacy MMA path of
+// this part has a long dependent-issue latency, so every warp keeps several independent
+// accumulators in flight.
+//
+// Both kernels are launched with programmatic stream serialisation and their producers request
+// the first weight tiles before they wait for the predecessor kernel (weights and plan are not
+// written by any kernel that can still be running), so a kernel's start-up overlaps its
+// predecessor's tail.
 //
 // shrink: weight rows are the M rows, the unit's <= 8 tokens the N columns.  Consecutive units
 // of one (projection, work segment) are accumulated in registers; when the run ends the CTA
-// publishes ONE split-K partial, marks its slot in a bit mask and adds the run length to an
-// arrival counter.  The CTA that completes the count folds the marked slots in ascending
-// order, so results are bit-reproducible.
-// expand: tokens are the M rows - rows 0..7 carry the hi halves of the fp32 intermediate, rows
-// 8..15 the lo halves, so one MMA yields both products - and 8 output rows of B are the N
-// columns; results are added into the staged y tile, which is written back with coalesced
-// 16-byte stores.
+// writes ONE split-K partial into the slot numbered by the run's first unit.  Which slots a
+// segment has follows from the CTAs' ranges alone, so there are no counters, flags or fences:
+// the kernel boundary publishes the partials.
+// expand: the first unit a CTA has of a segment brings the intermediate along: its producer
+// adds up the segment's slots in ascending k order (bit-reproducible) straight into the stage.
+// The weight tile is the MMA's A operand (16 output columns x 16 rank indices), the N columns
+// hold the hi and lo 16-bit halves of four tokens' fp32 intermediate, so one MMA is exact for
+// four tokens; results are added into the staged y tile, which each warp writes back itself.
 //
 // Every mbarrier wait is bounded: on expiry the thread records an error word in the workspace
 // and carries on with the same control flow, so the kernel always terminates.
@@ -31,28 +40,6 @@
 // Semantics: add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx, scale) of the
 // reference (lightllm/models/lora_gpu.py:138,150,162), pools as at :33-40.
 #include "lora_common.cuh"
-
-#ifdef B200_LORA_TIMELINE
-// Tuning aid (never in the shipped build): consumer thread 0 of every CTA stamps each item.
-__device__ unsigned long long g_timeline[512][96][12];
-__device__ int g_tl_slot;
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-extern "C" int b200_lora_debug_timeline(void* host) { return (int)cudaMemcpyFromSymbol(host, g_timeline, sizeof(g_timeline)); }
-#define TL(slot, k, v) { if (tid == 0 && (slot) < 96 && blockIdx.x < 512) g_timeline[blockIdx.x][slot][k] = (v); }
-// clock stamp k of the item the calling consumer is working on (slot kept in a register by the loop)
-#define TLC(k) { if (tid == 0 && tl_slot < 96 && blockIdx.x < 512) g_timeline[blockIdx.x][tl_slot][k] = (unsigned long long)clock64(); }
-#define TLC_ARG , int tl_slot
-#define TLC_PASS , n + 1
-#define TLC_FWD , tl_slot
-#define TLN(k) { const int tl_slot = n + 1; TLC(k) }
-#else
-#define TL(slot, k, v)
-#define TLC(k)
-#define TLC_ARG
-#define TLC_PASS
-#define TLC_FWD
-#define TLN(k)
-#endif
 
 namespace b200lora {
 
@@ -298,7 +285,7 @@ __device__ __forceinline__ int record_of_meta(const Meta& m, int lane) {
 // warps = (1, 2 or 4 row blocks) x (8, 4 or 2 slices of the unit's columns); a warp adds 4 MMAs
 // per unit into four independent accumulators that live across the units of one run.
 template <typename T, int R>
-__device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid TLC_ARG) {
+__device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid) {
     constexpr int MB = R >= 16 ? R / 16 : 1;               // 16-row blocks: 1, 1, 2, 4
     constexpr int KSPLIT = kConsWarps / MB;                // 8, 8, 4, 2
     constexpr int KC_COLS = R <= 16 ? 512 : R == 32 ? 256 : 128;
@@ -307,7 +294,6 @@ __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned cha
     const int kslot = warp % KSPLIT, mblk = warp / KSPLIT;
     const int g = lane >> 2, t = lane & 3;
     const unsigned char* xrow = stage + kWTile + g * (KC_COLS * 2 + kXPad) + t * 16;
-    TLC(6)
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb) {                        // every warp owns two 32-column blocks
         const int col = (kslot * 2 + kb) * 32;
@@ -322,15 +308,14 @@ __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned cha
             Mma<T>::run(acc[2 * kb + 1], w.z, u.z, w.w, u.w, xb.z, xb.w);
         }
     }
-    TLC(7)
 }
 template <typename T>
-__device__ __forceinline__ void shrink_consume_any(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid TLC_ARG) {
+__device__ __forceinline__ void shrink_consume_any(const Meta& m, const unsigned char* stage, float (&acc)[4][4], int tid) {
     switch (m.u.rank) {
-        case 8:  shrink_consume<T, 8>(m, stage, acc, tid TLC_FWD); break;
-        case 16: shrink_consume<T, 16>(m, stage, acc, tid TLC_FWD); break;
-        case 32: shrink_consume<T, 32>(m, stage, acc, tid TLC_FWD); break;
-        default: shrink_consume<T, 64>(m, stage, acc, tid TLC_FWD); break;
+        case 8:  shrink_consume<T, 8>(m, stage, acc, tid); break;
+        case 16: shrink_consume<T, 16>(m, stage, acc, tid); break;
+        case 32: shrink_consume<T, 32>(m, stage, acc, tid); break;
+        default: shrink_consume<T, 64>(m, stage, acc, tid); break;
     }
 }
 
@@ -524,7 +509,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
                 run.proj = m.proj; run.wseg = m.u.wseg; run.start = m.u.start; run.ntok = m.u.ntok;
                 run.rank = m.u.rank; run.first_kc = m.kc; run.count = 0; run.n_chunks = m.n_chunks;
             }
-            shrink_consume_any<T>(m, smem + s * kShrinkStage, acc, tid TLC_PASS);
+            shrink_consume_any<T>(m, smem + s * kShrinkStage, acc, tid);
             ++run.count;
         }
         __syncwarp();
@@ -620,7 +605,7 @@ __device__ __forceinline__ unsigned hl_pack(float v0, float v1, bool lo) {
 // columns back, so the consumer warps never meet at a barrier.
 template <typename T, int R>
 __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid,
-                                               unsigned (&bf)[2][4][2], bool reuse TLC_ARG) {
+                                               unsigned (&bf)[2][4][2], bool reuse) {
     constexpr int KS = R == 64 ? 4 : R == 32 ? 2 : 1;
     constexpr int JC = kSuper / (R <= 16 ? 4 : R / 4);
     constexpr int NBW = JC / 16 / kConsWarps;              // 16-column blocks per warp: 4, 4, 2, 1
@@ -671,7 +656,6 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
     }
     }
 
-    TLC(6)
     const int jbase = warp * NBW * 16;
     float acc[NBW][2][4];
 #pragma unroll
@@ -711,7 +695,6 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
         }
     }
 
-    TLC(7)
     // Token t (+4): hi + lo products for columns g and g + 8.  Lanes g and g ^ 1 swap one value
     // so that each ends up with two adjacent columns: (g, g+1) for even g, (g+7, g+8) for odd g.
     unsigned char* ysb = stage + kWTile;
@@ -790,7 +773,6 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
             }
         }
     }
-    TLC(8)
     if (staged) {
         // the warp writes its own columns of the updated y tile back, 16 bytes per lane
         __syncwarp();
@@ -803,7 +785,6 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
             }
         }
     }
-    TLC(9)
 }
 
 template <typename T>
@@ -891,10 +872,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             const bool reuse = key == bf_key;
             bf_key = key;
             switch (m.u.rank) {
-                case 8:  expand_consume<T, 8>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                case 16: expand_consume<T, 16>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                case 32: expand_consume<T, 32>(p, m, stage, tid, bf, reuse TLC_PASS); break;
-                default: expand_consume<T, 64>(p, m, stage, tid, bf, reuse TLC_PASS); break;
+                case 8:  expand_consume<T, 8>(p, m, stage, tid, bf, reuse); break;
+                case 16: expand_consume<T, 16>(p, m, stage, tid, bf, reuse); break;
+                case 32: expand_consume<T, 32>(p, m, stage, tid, bf, reuse); break;
+                default: expand_consume<T, 64>(p, m, stage, tid, bf, reuse); break;
             }
         }
         __syncwarp();

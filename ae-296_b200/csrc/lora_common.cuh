@@ -100,11 +100,9 @@ __host__ __device__ inline PlanView plan_view(void* base, int cap, int n_adapter
 // control words (zero at rest), then the reduced intermediate v [n_proj][cap][64] fp32, then
 // the split-K partials [n_kchunk][n_proj][cap][64] fp32.
 struct WorkspaceCtl {
-    unsigned ticket[2];       // dynamic work tickets: shrink, expand
-    unsigned done[2];         // CTAs that have drained their queue
+    unsigned reserved0[4];
     unsigned error;           // sticky device-side error word
-    unsigned pad[10];
-    unsigned epoch;           // launches of the fused kernel so far; v-ready flags hold epoch + 1
+    unsigned reserved1[11];
 };
 static_assert(sizeof(WorkspaceCtl) == 64, "control block is 16 words");
 
@@ -112,8 +110,11 @@ __host__ __device__ inline int max_kchunks(int h_in) { return (h_in + 127) / 128
 
 __host__ __device__ inline size_t ws_counter_words(int cap) { return (size_t)kMaxProj * cap; }
 
+// control block and arrival counters: what must be zero before the first launch
+__host__ __device__ inline size_t ws_ctl_bytes(int cap) { return sizeof(WorkspaceCtl) + 4 * ((ws_counter_words(cap) + 3) & ~size_t(3)); }
+
 __host__ __device__ inline size_t workspace_bytes(int cap, int n_proj, int max_h_in) {
-    size_t ctl = sizeof(WorkspaceCtl) + 8 * ((ws_counter_words(cap) + 3) & ~size_t(3)) + 8 * ws_counter_words(cap);
+    size_t ctl = ws_ctl_bytes(cap);
     size_t v = (size_t)n_proj * cap * kMaxRank * 4;
     size_t part = (size_t)max_kchunks(max_h_in) * n_proj * cap * kMaxRank * 4;
     return ctl + v + part + 256;
@@ -121,9 +122,7 @@ __host__ __device__ inline size_t workspace_bytes(int cap, int n_proj, int max_h
 
 struct WorkspaceView {
     WorkspaceCtl* ctl;
-    unsigned* counters;   // [kMaxProj][cap]  arrivals per (projection, work segment)
-    unsigned long long* masks;   // [kMaxProj][cap]  split-K slots published per (projection, work segment)
-    unsigned* ready;      // [kMaxProj][cap]  epoch + 1 once v of (projection, work segment) is final (fused kernel)
+    unsigned* counters;   // [kMaxProj][cap]  arrivals per (projection, work segment); general-path kernels only
     float* v;             // [n_proj][cap][64]
     float* partial;       // [kchunk][n_proj][cap][64]
 };
@@ -133,8 +132,6 @@ __host__ __device__ inline WorkspaceView workspace_view(void* base, int cap, int
     WorkspaceView w;
     w.ctl = reinterpret_cast<WorkspaceCtl*>(p);            p += sizeof(WorkspaceCtl);
     w.counters = reinterpret_cast<unsigned*>(p);           p += 4 * ((ws_counter_words(cap) + 3) & ~size_t(3));
-    w.masks = reinterpret_cast<unsigned long long*>(p);    p += 8 * ws_counter_words(cap);
-    w.ready = reinterpret_cast<unsigned*>(p);              p += 4 * ((ws_counter_words(cap) + 3) & ~size_t(3));
     p = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(p) + 127) & ~uintptr_t(127));
     w.v = reinterpret_cast<float*>(p);                     p += (size_t)n_proj * cap * kMaxRank * 4;
     w.partial = reinterpret_cast<float*>(p);

@@ -5,7 +5,7 @@
 Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM (CUDA-graph
 replay of the whole pass, CUDA-event timed, max over ranks); `e2e` is the same pass driven
 from pinned host buffers through the public ops, host<->device copies inside the timed
-region; `roofline` is the fused shrink->expand kernel (the pass without the plan kernel);
+region; `roofline` is the shrink + expand kernel pair (the pass without the plan kernel);
 `cpu_baseline` is the reference's CPU LoRA arithmetic timed on this host's cores.
 With N > 1 each rank holds its own adapters and batch (placement by adapter, no collective).
 """
@@ -22,6 +22,10 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+
+# DRAM bytes per kernel launch of workload 1, from the ncu capture summarised in
+# profiles/bgmv_cfg1_ncu.md (None until that capture exists for the current kernels)
+TRAFFIC_PER_LAUNCH = None
 
 
 def parse():
@@ -256,7 +260,8 @@ def main():
             batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l, flags)
             batch.apply([(x_o[l], ys["o"][l], pools["o"])], l, flags)
 
-    launches_per_pass = 1 + n_layers * (4 if use_tiles else 2)
+    # per layer two applies (q/k/v, o), each a shrink and an expand launch (plus the tile launch)
+    launches_per_pass = 1 + n_layers * (6 if use_tiles else 4)
 
     def capture(flags=0, plan=True):
         g = torch.cuda.CUDAGraph()
@@ -313,28 +318,31 @@ def main():
     e = 2
     exp_bytes = sum(rsum * p.h_out * e + 2 * T * p.h_out * e for p in wl.projections) * n_layers
     shr_bytes = sum(rsum * p.h_in * e + T * p.h_in * e + 4 * T for p in wl.projections) * n_layers
-    # dominant kernel: the fused shrink->expand BGMV kernel (one launch per apply); timed as the whole
-    # pass without the plan kernel.  The two halves are also timed alone (separate kernels).
+    # dominant kernels: the shrink and the expand BGMV kernel, one launch of each per apply; timed
+    # together as the whole pass without the plan kernel, and each half alone (the lone shrink half
+    # also runs the small kernel that writes the intermediate out for tensor-parallel callers).
     ms_noplan = timed(capture(0, plan=False), args.steps, 3)
     ms_exp = timed(capture(_lib.ONLY_EXPAND, plan=False), args.steps, 3)
     ms_shr = timed(capture(_lib.ONLY_SHRINK, plan=False), args.steps, 3)
     us_plan = timed(capture_plan_only(), args.steps, 3) * 1e3 / 8
     ms_dta = timed(capture(_lib.DELTA_THEN_ADD, plan=False), args.steps, 3)
-    n_launch = n_layers * 2
+    n_apply = n_layers * 2
+    n_launch = n_apply * 2
     pass_bytes = wl.bytes_per_layer() * n_layers
-    # DRAM bytes per launch from the ncu capture summarised in profiles/bgmv_fused_cfg1_ncu.md
-    # (dram__bytes_read.sum + dram__bytes_write.sum, mean of the q/k/v and the o launch of one layer)
-    traffic = 83.1e6 if (wl.cfg == 1 and not use_tiles) else None
+    # DRAM bytes per launch from the ncu capture summarised in profiles/bgmv_cfg1_ncu.md
+    # (dram__bytes_read.sum + dram__bytes_write.sum, mean over the four launches of one layer)
+    traffic = TRAFFIC_PER_LAUNCH if (wl.cfg == 1 and not use_tiles) else None
     ach = pass_bytes / (ms_noplan * 1e-3) / 1e9
     roofline = {
-        "bound": "hbm", "kernel": "bgmv_fused_tma_kernel" if not use_tiles else "sgmv_tile_kernel + bgmv_fused_tma_kernel",
+        "bound": "hbm",
+        "kernel": ("" if not use_tiles else "sgmv_tile_kernel + ") + "bgmv_shrink_tma_kernel + bgmv_expand_tma_kernel",
         "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
         "peak_source": peak_src, "bytes_per_launch": pass_bytes / n_launch,
         "us_per_launch": ms_noplan * 1e3 / n_launch, "frac_of_8TBs_nominal": ach / 8000.0,
         "expand_half": {"achieved": exp_bytes / (ms_exp * 1e-3) / 1e9, "frac": exp_bytes / (ms_exp * 1e-3) / 1e9 / peak,
-                        "us_per_launch": ms_exp * 1e3 / n_launch},
+                        "us_per_launch": ms_exp * 1e3 / n_apply},
         "shrink_half": {"achieved": shr_bytes / (ms_shr * 1e-3) / 1e9, "frac": shr_bytes / (ms_shr * 1e-3) / 1e9 / peak,
-                        "us_per_launch": ms_shr * 1e3 / n_launch},
+                        "us_per_launch": ms_shr * 1e3 / n_apply},
         "plan_us": us_plan,
         # optional mode with the reference's `q += q_lora` rounding (delta rounded, then a 16-bit add)
         "delta_then_add_mode": {"achieved": pass_bytes / (ms_dta * 1e-3) / 1e9,

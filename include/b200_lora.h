@@ -50,9 +50,9 @@ enum {
     B200_LORA_MID_ROUND = 1,   /* round the [T, r] intermediate to the I/O type, as the reference's
                                   batched-matmul prefill op does (lightllm/models/lora_gpu.py:127-128) */
     B200_LORA_NO_TENSOR = 2,   /* keep tall segments on the BGMV kernels too (no tcgen05 tiles) */
-    B200_LORA_ONLY_SHRINK = 4, /* tensor parallel / profiling: run only the shrink half (v is left in the workspace) */
-    B200_LORA_ONLY_EXPAND = 8, /* profiling: run only the expand half on the workspace's current v */
-    B200_LORA_TWO_KERNELS = 16, /* run shrink and expand as two launches instead of the fused kernel */
+    B200_LORA_ONLY_SHRINK = 4, /* tensor parallel: run only the shrink half; the intermediate v is left in the
+                                  workspace (b200_lora_workspace_v_region) for the caller to sum over ranks */
+    B200_LORA_ONLY_EXPAND = 8, /* tensor parallel: run only the expand half on the workspace's current v */
     B200_LORA_DELTA_THEN_ADD = 32 /* 16-bit y only: round the delta to the I/O type and add it to y in that
                                    type, as the reference's `q += q_lora` does
                                    (lightllm/models/llama/layer_infer/transformer_layer_infer.py:160-170).
