@@ -282,8 +282,12 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
         if ((projs[i].h_in % 256) || (projs[i].h_out % 256) || projs[i].h_in > 8192) fast = false;
     if (fast) {
         for (int i = 0; i < n_proj && fast; ++i)
-            fast = tensor_map_2d(&p.amap[i], projs[i].wa, (uint64_t)projs[i].h_in, pool_rows(adapters), 128, 8,
-                                 CU_TENSOR_MAP_SWIZZLE_NONE);
+            for (int c = 0; c < 4 && fast; ++c) {
+                const uint32_t rc = 8u << c;
+                if (!adapters->packed && rc != (uint32_t)adapters->r_pool) continue;    // dense pools have one rank
+                fast = tensor_map_2d(&p.amap[i][c], projs[i].wa, (uint64_t)projs[i].h_in, pool_rows(adapters), 128, rc,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE);
+            }
     }
     if (e == cudaSuccess) e = fast ? launch_bgmv_tma(p, io_dtype, n_sm, s) : launch_bgmv(p, io_dtype, n_sm, s);
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);

@@ -7,7 +7,7 @@
 // A CTA is two producer warps plus eight consumer warps around a 4-stage shared-memory ring;
 // two CTAs share an SM, so ~100 KB of loads per SM are in flight.  The producers walk the range
 // (alternate units each) and fill a stage with ONE instruction per kind:
-//   shrink  A rows [r, KC]   -> up to eight [8 x 128] boxes of a 2-D tensor map over the A pool
+//   shrink  A rows [r, KC]   -> one [r x 128] box of a 2-D tensor map over the A pool per 128 columns
 //           x rows [ntok, KC]-> one bulk copy per token
 //   expand  B rows [JC, r]   -> one contiguous bulk copy; plus one copy per token for the y
 //           tile that will be updated
@@ -52,8 +52,7 @@ constexpr int kConsThreads = kConsWarps * 32;
 constexpr int kProdWarps = 2;                     // producer warps take alternate items
 constexpr int kThreads = kConsThreads + kProdWarps * 32;
 constexpr int kCtasPerSm = 2;
-constexpr int kBoxCols = 128, kBoxRows = 8;       // shrink weight box: 2 KB
-constexpr int kBoxBytes = kBoxCols * kBoxRows * 2;
+constexpr int kBoxCols = 128;                     // columns of a shrink weight box; its rows are the adapter's rank rows
 constexpr int kWTile = 16384;                     // weight tile of one unit
 constexpr int kXPad = 64;                         // bytes added to an x-tile row (bank spread)
 constexpr int kXBytes = 8 * (512 * 2 + kXPad);
@@ -239,7 +238,7 @@ __device__ __forceinline__ long long item_row0(const ApplyParams& p, const Item&
 // =============================================================================================
 // shrink
 // =============================================================================================
-// Stage layout: weight boxes b = (row group) * ncb + (column block), each [8 rows x 128 cols]
+// Stage layout: one weight box per 128-column block of the unit, each [r rows x 128 cols]
 // contiguous (row pitch 256 B); then the x tile, one row per token, pitch KC*2 + 64 bytes.
 // `parts` bit 0: the barrier's byte count and the weight boxes (never written while kernels of
 // this library run, so they may be requested before the predecessor kernel has ended); bit 1:
@@ -250,17 +249,15 @@ __device__ __forceinline__ void shrink_produce(const ApplyParams& p, const Item&
     const ProjArgs& pj = p.proj[m.proj];
     const int r = m.rank;
     const int kc_cols = kSuper / n_sub(r);                // 512, 512, 256, 128
-    const int ncb = kc_cols / kBoxCols;                   // 4, 4, 2, 1
-    const int nbox = ncb * (r / kBoxRows);                // 4, 8, 8, 8
+    const int ncb = kc_cols / kBoxCols;                   // boxes of the unit: 4, 4, 2, 1
+    const int box_bytes = r * kBoxCols * 2;
+    const int cls = r <= 8 ? 0 : r <= 16 ? 1 : r <= 32 ? 2 : 3;
     const unsigned row_bytes = m.width_ok * 2;
     if (parts & 1) {
-        if (lane == 0) mbar_arrive_expect_tx(bar, nbox * kBoxBytes + m.ntok * row_bytes);
+        if (lane == 0) mbar_arrive_expect_tx(bar, ncb * box_bytes + m.ntok * row_bytes);
         __syncwarp();
-        if (lane < nbox) {
-            const int rg = lane / ncb, cb = lane - rg * ncb;
-            tensor_g2s_2d(stage + lane * kBoxBytes, &p.amap[m.proj], m.c0 + cb * kBoxCols,
-                          (int)item_row0(p, m) + rg * kBoxRows, bar);
-        }
+        if (lane < ncb)
+            tensor_g2s_2d(stage + lane * box_bytes, &p.amap[m.proj][cls], m.c0 + lane * kBoxCols, (int)item_row0(p, m), bar);
     }
     // lanes 8..15 hold the token rows of the unit record
     if ((parts & 2) && lane >= 8 && lane < 8 + m.ntok)
@@ -289,7 +286,6 @@ __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned cha
     constexpr int MB = R >= 16 ? R / 16 : 1;               // 16-row blocks: 1, 1, 2, 4
     constexpr int KSPLIT = kConsWarps / MB;                // 8, 8, 4, 2
     constexpr int KC_COLS = R <= 16 ? 512 : R == 32 ? 256 : 128;
-    constexpr int NCB = KC_COLS / kBoxCols;
     const int lane = tid & 31, warp = tid >> 5;
     const int kslot = warp % KSPLIT, mblk = warp / KSPLIT;
     const int g = lane >> 2, t = lane & 3;
@@ -299,11 +295,11 @@ __device__ __forceinline__ void shrink_consume(const Meta& m, const unsigned cha
         const int col = (kslot * 2 + kb) * 32;
         if (col < m.width_ok) {
             const int cb = col >> 7, cin = col & 127;
-            const unsigned char* wbox = stage + ((mblk * 2) * NCB + cb) * kBoxBytes + g * 256 + cin * 2 + t * 16;
+            const unsigned char* wbox = stage + cb * (R * kBoxCols * 2) + (mblk * 16 + g) * 256 + cin * 2 + t * 16;
             const uint4 xb = *reinterpret_cast<const uint4*>(xrow + col * 2);
             const uint4 w = *reinterpret_cast<const uint4*>(wbox);
             uint4 u = make_uint4(0u, 0u, 0u, 0u);
-            if (R >= 16) u = *reinterpret_cast<const uint4*>(wbox + NCB * kBoxBytes);   // rank 8 has no rows 8..15
+            if (R >= 16) u = *reinterpret_cast<const uint4*>(wbox + 8 * 256);           // rank 8 has no rows 8..15
             Mma<T>::run(acc[2 * kb], w.x, u.x, w.y, u.y, xb.x, xb.y);
             Mma<T>::run(acc[2 * kb + 1], w.z, u.z, w.w, u.w, xb.z, xb.w);
         }

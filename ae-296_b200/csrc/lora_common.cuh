@@ -150,7 +150,8 @@ struct ProjArgs {
 };
 
 struct ApplyParams {
-    alignas(64) CUtensorMap amap[kMaxProj];   // 2-D maps over the A pools ([rows, h_in], box 128 x 8); TMA kernels only
+    alignas(64) CUtensorMap amap[kMaxProj][4];   // 2-D maps over the A pools ([rows, h_in]), box 128 columns x (8, 16, 32, 64) rows
+                                              // by rank class: all rank rows of an adapter in one copy; TMA kernels only
     ProjArgs proj[kMaxProj];
     int n_proj;
     int total_super_in, total_super_out;
