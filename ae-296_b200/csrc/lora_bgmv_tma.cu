@@ -597,8 +597,7 @@ __device__ __forceinline__ unsigned hl_pack(float v0, float v1, bool lo) {
 // with the hi and lo products of token t for output columns g and g + 8 of the block.
 //   R=64: chunks 2t and 2t+1 of each 128-byte weight row (4 MMA k-steps)
 //   R=32: chunk t of each 64-byte row (2 k-steps);  R=16: 8 bytes (1 k-step);  R=8: 4 bytes.
-// A warp owns NBW consecutive 16-column blocks and, for a staged 16-bit y, writes its own
-// columns back, so the consumer warps never meet at a barrier.
+// A warp owns NBW consecutive 16-column blocks; the consumer warps never meet at a barrier.
 template <typename T, int R>
 __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, unsigned char* stage, int tid,
                                                unsigned (&bf)[2][4][2], bool reuse) {
@@ -714,28 +713,27 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
     }
     const bool col_ok = jbase < m.width_ok;                // the warp's columns lie inside the matrix
     if (staged) {
-        // all of the lane's y pairs are read before the first one is written back
-        unsigned yw[NBW][2];
+        // the staged y tile is only read: every lane adds its pairs and stores them straight to
+        // global memory, eight lanes filling one 32-byte sector of a token's row
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
-            const unsigned* yp = reinterpret_cast<const unsigned*>(ysb + (t + 4 * grp) * ypitch + jl * 2);
+            const int q = t + 4 * grp;
+            if (grp < ngrp && q < ntok && col_ok) {
+                const unsigned* ys = reinterpret_cast<const unsigned*>(ysb + q * ypitch + jl * 2);
+                unsigned* yg = reinterpret_cast<unsigned*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[q] * pj.ldy + m.c0 + jl);
+                unsigned yw[NBW];
 #pragma unroll
-            for (int nb = 0; nb < NBW; ++nb) yw[nb][grp] = (grp < ngrp) ? yp[nb * 8] : 0u;
-        }
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-            if (grp < ngrp && t + 4 * grp < ntok && col_ok) {
-                unsigned* yp = reinterpret_cast<unsigned*>(ysb + (t + 4 * grp) * ypitch + jl * 2);
+                for (int nb = 0; nb < NBW; ++nb) yw[nb] = ys[nb * 8];
 #pragma unroll
                 for (int nb = 0; nb < NBW; ++nb) {
                     float lo, hi;
                     if (Cvt<T>::is_bf16) {
-                        lo = __uint_as_float(yw[nb][grp] << 16); hi = __uint_as_float(yw[nb][grp] & 0xffff0000u);
+                        lo = __uint_as_float(yw[nb] << 16); hi = __uint_as_float(yw[nb] & 0xffff0000u);
                     } else {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&yw[nb][grp]));
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&yw[nb]));
                         lo = f.x; hi = f.y;
                     }
-                    yp[nb * 8] = Cvt<T>::pack2(lo + d0[nb][grp], hi + d1[nb][grp]);
+                    yg[nb * 8] = Cvt<T>::pack2(lo + d0[nb][grp], hi + d1[nb][grp]);
                 }
             }
         }
@@ -766,18 +764,6 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
                         else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
                     }
                 }
-            }
-        }
-    }
-    if (staged) {
-        // the warp writes its own columns of the updated y tile back, 16 bytes per lane
-        __syncwarp();
-        constexpr int CPR = NBW * 2;                       // 16-byte chunks per token row: 8, 8, 4, 2
-        if (jbase < m.width_ok) {
-            for (int idx = lane; idx < ntok * CPR; idx += 32) {
-                const int row = idx / CPR, c = idx % CPR;
-                const uint4 val = *reinterpret_cast<const uint4*>(ysb + row * ypitch + jbase * 2 + c * 16);
-                *reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)m.u.tok[row] * pj.ldy + m.c0 + jbase + c * 8) = val;
             }
         }
     }
