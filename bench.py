@@ -24,8 +24,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # DRAM bytes per kernel launch of workload 1, from the ncu capture summarised in
-# profiles/bgmv_cfg1_ncu.md (None until that capture exists for the current kernels)
-TRAFFIC_PER_LAUNCH = None
+# profiles/bgmv_cfg1_ncu.md: mean of dram__bytes_read.sum + dram__bytes_write.sum over the four
+# launches of one layer
+TRAFFIC_PER_LAUNCH = 41.2e6
 
 
 def parse():
