@@ -9,11 +9,12 @@
 //   phase 2   D2[128, 128]  = V . B[n0:n0+128, :]^T        per 128-column slice of the output
 //   epilogue  y[rows, n0:n0+128] += scale * D2
 //
-// Warp roles: warp 0 issues TMA tensor copies (x and A boxes for phase 1, B boxes for phase 2)
-// into mbarrier-tracked rings; warp 1 allocates TMEM and has one thread issue every
-// tcgen05.mma, releasing ring slots and publishing accumulators with tcgen05.commit; warps 2..5
-// read accumulators with tcgen05.ld (each warp its own 32-lane quadrant of TMEM) and do the
-// conversion and the y update.  Operand tiles use the 128/64/32-byte swizzled K-major layouts
+// Warp roles: warps 0 and 3 issue TMA tensor copies (x and A boxes for phase 1, B boxes for
+// phase 2) into mbarrier-tracked rings; warp 1 allocates TMEM and has one thread issue the tcgen05.mma of
+// phase 1 into one of two D1 buffers, one item ahead; warp 2 has one thread issue those of phase
+// 2; both release ring slots and publish accumulators with tcgen05.commit; warps 4..11 read
+// accumulators with tcgen05.ld (each warp its own 32-lane quadrant of TMEM, two warps per
+// quadrant sharing a slice's columns) and do the conversion and the y update.  Operand tiles use the 128/64/32-byte swizzled K-major layouts
 // that TMA writes and the MMA descriptors name.  Two D2 buffers let the MMA of slice n+1 overlap
 // the epilogue of slice n.  Single-CTA launch; every copy reads this GPU's own memory.
 //
@@ -40,11 +41,12 @@ constexpr int kStage1 = kXTile + kATile;
 constexpr int kBTile = kBN * 64 * 2;             // 16 KB (rank 64)
 constexpr int kVTile = kBM * 64 * 2;             // 16 KB
 constexpr int kSmemTiles = kS1 * kStage1 + kS2 * kBTile + 2 * kVTile;
-constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 4 + 4;
+constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 6 + 4;
 constexpr int kSgmvSmem = kSmemTiles + kNumBars * 8 + 64 + 1024;     // + alignment slack
-constexpr int kSgmvThreads = 192;
+constexpr int kEpiWarps = 8;         // two per TMEM lane quadrant: each takes half the columns of a slice
+constexpr int kSgmvThreads = 128 + kEpiWarps * 32;   // phase-1 TMA, phase-1 MMA, phase-2 MMA, phase-2 TMA, epilogue
 constexpr int kTmemCols = 512;
-constexpr int kD1Col = 0, kD2Col = 64;
+constexpr int kD1Col = 0, kD2Col = 128;     // two D1 buffers of 64 columns, two D2 buffers of 128
 constexpr unsigned kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -168,8 +170,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + kNumBars);
     // barrier indices
     const int FULL1 = 0, EMPTY1 = kS1, FULL2 = 2 * kS1, EMPTY2 = 2 * kS1 + kS2;
-    const int D1_FULL = 2 * kS1 + 2 * kS2, D1_EMPTY = D1_FULL + 1, V_READY = D1_FULL + 2, V_FREE = D1_FULL + 3;
-    const int D2_FULL = D1_FULL + 4, D2_EMPTY = D1_FULL + 6;
+    const int D1_FULL = 2 * kS1 + 2 * kS2, D1_EMPTY = D1_FULL + 2, V_READY = D1_FULL + 4, V_FREE = D1_FULL + 5;
+    const int D2_FULL = D1_FULL + 6, D2_EMPTY = D1_FULL + 8;
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     pdl_wait_prior();
@@ -195,11 +197,10 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     if (tid == 0) {
         for (int s = 0; s < kS1; ++s) { mbar_init(bar(FULL1 + s), 1); mbar_init(bar(EMPTY1 + s), 1); }
         for (int s = 0; s < kS2; ++s) { mbar_init(bar(FULL2 + s), 1); mbar_init(bar(EMPTY2 + s), 1); }
-        mbar_init(bar(D1_FULL), 1);
-        mbar_init(bar(D1_EMPTY), 128);
+        for (int b = 0; b < 2; ++b) { mbar_init(bar(D1_FULL + b), 1); mbar_init(bar(D1_EMPTY + b), 128); }
         mbar_init(bar(V_READY), 128);
         mbar_init(bar(V_FREE), 1);
-        for (int b = 0; b < 2; ++b) { mbar_init(bar(D2_FULL + b), 1); mbar_init(bar(D2_EMPTY + b), 128); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar(D2_FULL + b), 1); mbar_init(bar(D2_EMPTY + b), kEpiWarps * 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                    // one warp owns the TMEM allocation
@@ -212,16 +213,15 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const unsigned tmem = *reinterpret_cast<volatile unsigned*>(tmem_slot);
 
     if (warp == 0) {
-        // ================= TMA producer =================
-        unsigned n1 = 0, n2 = 0;        // ring uses so far
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int part = item % nsplit, rest = item / nsplit;
+        // ================= TMA producer, phase 1: x and A boxes =================
+        unsigned n1 = 0;                // ring uses so far
+        for (int item = blockIdx.x; do1 && item < n_items; item += gridDim.x) {
+            const int rest = item / nsplit;
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
-            const ProjArgs& pj = p.proj[proj];
-            const int nkb = pj.h_in / kBK;
+            const int nkb = p.proj[proj].h_in / kBK;
             const int n_abox = t.rank / 8;
-            for (int kb = 0; do1 && kb < nkb; ++kb, ++n1) {
+            for (int kb = 0; kb < nkb; ++kb, ++n1) {
                 const int s = n1 % kS1;
                 mbar_wait(bar(EMPTY1 + s), ((n1 / kS1) & 1) ^ 1, err, 11);
                 const unsigned dst = smem_u32(stage1 + s * kStage1);
@@ -234,9 +234,19 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                     tensor_g2s_2d(dst + kXTile + lane * 1024, &sp.amap[proj], kb * kBK, (int)t.a_row0 + lane * 8,
                                   bar(FULL1 + s));
             }
+        }
+    } else if (warp == 3) {
+        // ================= TMA producer, phase 2: B boxes =================
+        // (a warp of its own: phase 1 runs an item ahead and must not queue behind these copies)
+        unsigned n2 = 0;
+        for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x) {
+            const int part = item % nsplit, rest = item / nsplit;
+            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const TileInfo t = tile_info(sp, p, pv, tile, proj);
+            const ProjArgs& pj = p.proj[proj];
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
             const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
-            for (int nt = nt0; do2 && nt < nnt; ++nt, ++n2) {
+            for (int nt = nt0; nt < nnt; ++nt, ++n2) {
                 const int s = n2 % kS2;
                 mbar_wait(bar(EMPTY2 + s), ((n2 / kS2) & 1) ^ 1, err, 12);
                 if (lane == 0) {
@@ -248,20 +258,22 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             }
         }
     } else if (warp == 1) {
-        // ================= MMA issuer =================
-        unsigned n1 = 0, n2 = 0, nd = 0, n_item = 0;
+        // ================= MMA issuer, phase 1: D1[item & 1] = X . A^T =================
+        // runs one item ahead of phase 2, so the x stream of the next item overlaps the y update
+        // of this one
+        unsigned n1 = 0, n_item = 0;
         const bool bf16 = Cvt<T>::is_bf16;
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
-            const int part = item % nsplit, rest = item / nsplit;
+        for (int item = blockIdx.x; do1 && item < n_items; item += gridDim.x, ++n_item) {
+            const int rest = item / nsplit;
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
-            const ProjArgs& pj = p.proj[proj];
-            const int nkb = pj.h_in / kBK;
-            // phase 1: D1 = X . A^T     (D1 must have been drained by the epilogue of the previous item)
-            if (do1) mbar_wait(bar(D1_EMPTY), (n_item & 1) ^ 1, err, 13);
+            const int nkb = p.proj[proj].h_in / kBK;
+            const int b1 = n_item & 1;
+            // the buffer must have been drained by the epilogue of the item two before
+            mbar_wait(bar(D1_EMPTY + b1), ((n_item >> 1) & 1) ^ 1, err, 13);
             tc_fence_after();
             const unsigned idesc1 = make_idesc(bf16, kBM, t.rank);
-            for (int kb = 0; do1 && kb < nkb; ++kb, ++n1) {
+            for (int kb = 0; kb < nkb; ++kb, ++n1) {
                 const int s = n1 % kS1;
                 mbar_wait(bar(FULL1 + s), (n1 / kS1) & 1, err, 14);
                 tc_fence_after();
@@ -269,15 +281,23 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                     const unsigned xa = smem_u32(stage1 + s * kStage1), aa = xa + kXTile;
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
-                        tc_mma_f16(tmem + kD1Col, make_desc(xa + k * 32, 2, 1024), make_desc(aa + k * 32, 2, 1024),
+                        tc_mma_f16(tmem + kD1Col + b1 * 64, make_desc(xa + k * 32, 2, 1024), make_desc(aa + k * 32, 2, 1024),
                                    idesc1, (kb | k) != 0);
                     tc_commit(bar(EMPTY1 + s));                       // slot reusable once these MMAs finish
-                    if (kb == nkb - 1) tc_commit(bar(D1_FULL));
+                    if (kb == nkb - 1) tc_commit(bar(D1_FULL + b1));
                 }
                 __syncwarp();
             }
-            // phase 2: D2[buf] = V . B_slice^T
-            if (!do2) continue;
+        }
+    } else if (warp == 2) {
+        // ================= MMA issuer, phase 2: D2[buf] = V . B_slice^T =================
+        unsigned n2 = 0, nd = 0, n_item = 0;
+        const bool bf16 = Cvt<T>::is_bf16;
+        for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x, ++n_item) {
+            const int part = item % nsplit, rest = item / nsplit;
+            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const TileInfo t = tile_info(sp, p, pv, tile, proj);
+            const ProjArgs& pj = p.proj[proj];
             mbar_wait(bar(V_READY), n_item & 1, err, 15);
             tc_fence_after();
             const unsigned layout = t.cls == 2 ? 2u : t.cls == 1 ? 4u : 6u;
@@ -311,6 +331,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     } else {
         // ================= epilogue warps =================
         const int quad = warp & 3;                          // TMEM lanes 32*quad .. +31
+        const int half = (warp - 4) >> 2;                   // which 64 columns of every 128-column slice
         const int row = quad * 32 + lane;
         const unsigned lane_base = (unsigned)(quad * 32) << 16;
         unsigned nd = 0, n_item = 0;
@@ -319,23 +340,26 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
-            // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes
+            if (half != 0 && !do2) continue;
+            // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes: first warp of the quadrant
+            if (half == 0) {
             float d1[64];
             float* vrow = ws.v + ((size_t)proj * p.cap + t.pos0 + row) * kMaxRank;
             if (do1) {
-                mbar_wait(bar(D1_FULL), n_item & 1, err, 18);
+                const int b1 = n_item & 1;
+                mbar_wait(bar(D1_FULL + b1), (n_item >> 1) & 1, err, 18);
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     if (c * 16 < t.rank) {
                         float v[16];
-                        tc_ld16(tmem + lane_base + kD1Col + c * 16, v);
+                        tc_ld16(tmem + lane_base + kD1Col + b1 * 64 + c * 16, v);
 #pragma unroll
                         for (int i = 0; i < 16; ++i) d1[c * 16 + i] = v[i];
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(bar(D1_EMPTY));
+                mbar_arrive(bar(D1_EMPTY + b1));
                 if (!do2) {                                  // shrink half only: publish the fp32 rows
                     if (row < t.valid) {
 #pragma unroll
@@ -379,6 +403,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> tensor-core reads
             mbar_arrive(bar(V_READY));
+            }
             // ---- D2 slices -> y
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
             const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
@@ -387,21 +412,21 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                 const int buf = nd & 1;
                 // the y slice of this row does not depend on the MMA: fetch all of it first, so
                 // sixteen loads are in flight while the accumulator is being produced
-                uint4 yv[kBN / 8];
+                uint4 yv[kBN / 16];
                 const bool pre = live && !p.y_f32;
-                uint4* yrow = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)(t.row0 + row) * pj.ldy + nt * kBN);
+                uint4* yrow = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)(t.row0 + row) * pj.ldy + nt * kBN) + half * (kBN / 16);
                 if (pre) {
 #pragma unroll
-                    for (int q = 0; q < kBN / 8; ++q)
-                        if (nt * kBN + q * 8 < pj.h_out) yv[q] = yrow[q];
+                    for (int q = 0; q < kBN / 16; ++q)
+                        if (nt * kBN + half * (kBN / 2) + q * 8 < pj.h_out) yv[q] = yrow[q];
                 }
                 mbar_wait(bar(D2_FULL + buf), (nd >> 1) & 1, err, 20);
                 tc_fence_after();
 #pragma unroll
-                for (int c = 0; c < kBN / 16; ++c) {
+                for (int c = 0; c < kBN / 32; ++c) {
                     float v[16];
-                    tc_ld16(tmem + lane_base + kD2Col + buf * kBN + c * 16, v);
-                    const int col = nt * kBN + c * 16;
+                    tc_ld16(tmem + lane_base + kD2Col + buf * kBN + half * (kBN / 2) + c * 16, v);
+                    const int col = nt * kBN + half * (kBN / 2) + c * 16;
                     if (live && col < pj.h_out) {
                         if (p.y_f32) {
                             float4* yp = reinterpret_cast<float4*>(reinterpret_cast<float*>(pj.y) +
