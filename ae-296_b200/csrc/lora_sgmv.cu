@@ -181,15 +181,23 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     unsigned* err = &ws.ctl->error;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_tiles = (hdr.error || hdr.cap != p.cap) ? 0 : hdr.n_tiles;
-    // fewer tiles than SMs: cut each tile's output columns into `nsplit` parts handled by different
-    // CTAs (each redoes the cheap phase 1 from L2), aiming at >= 2 items per CTA
+    // Work items: (tile, projection) pairs, dealt to the CTAs round by round.  The pairs of the
+    // last, incomplete round are cut by output columns into `nsplit` parts each (every part redoes
+    // the cheap phase 1, mostly from L2), so that the round keeps all SMs busy for a fraction of a
+    // pair's time instead of a few SMs for all of it.
     const int base_items = n_tiles * p.n_proj;
+    const int n_cta = (int)gridDim.x;
+    const int n_full = (base_items / n_cta) * n_cta, n_rem = base_items - n_full;
     int nsplit = 1;
-    if (base_items > 0 && base_items < (int)gridDim.x && !(p.flags & B200_LORA_ONLY_SHRINK))
-        nsplit = min(8, max(1, (2 * (int)gridDim.x + base_items - 1) / base_items));
+    if (n_rem > 0 && !(p.flags & B200_LORA_ONLY_SHRINK)) nsplit = min(8, max(1, (2 * n_cta) / n_rem));
     for (int i = 0; i < p.n_proj; ++i)                    // every part must own at least one column slice
         nsplit = min(nsplit, (p.proj[i].h_out + kBN - 1) / kBN);
-    const int n_items = base_items * nsplit;
+    const int n_items = n_full + n_rem * nsplit;
+    // item -> pair, part, parts of the pair
+    auto decode = [&](int item, int& rest, int& part, int& parts) {
+        if (item < n_full) { rest = item; part = 0; parts = 1; }
+        else { const int j = item - n_full; rest = n_full + j / nsplit; part = j % nsplit; parts = nsplit; }
+    };
     const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
     // tensor-parallel callers run the two halves separately and sum v in between
     const bool do1 = !(p.flags & B200_LORA_ONLY_EXPAND), do2 = !(p.flags & B200_LORA_ONLY_SHRINK);
@@ -216,7 +224,9 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         // ================= TMA producer, phase 1: x and A boxes =================
         unsigned n1 = 0;                // ring uses so far
         for (int item = blockIdx.x; do1 && item < n_items; item += gridDim.x) {
-            const int rest = item / nsplit;
+            int rest, part, parts;
+            decode(item, rest, part, parts);
+            (void)part;
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const int nkb = p.proj[proj].h_in / kBK;
@@ -240,12 +250,13 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         // (a warp of its own: phase 1 runs an item ahead and must not queue behind these copies)
         unsigned n2 = 0;
         for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x) {
-            const int part = item % nsplit, rest = item / nsplit;
+            int rest, part, parts;
+            decode(item, rest, part, parts);
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
-            const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
+            const int nt0 = part * nnt_all / parts, nnt = (part + 1) * nnt_all / parts;
             for (int nt = nt0; nt < nnt; ++nt, ++n2) {
                 const int s = n2 % kS2;
                 mbar_wait(bar(EMPTY2 + s), ((n2 / kS2) & 1) ^ 1, err, 12);
@@ -264,7 +275,9 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         unsigned n1 = 0, n_item = 0;
         const bool bf16 = Cvt<T>::is_bf16;
         for (int item = blockIdx.x; do1 && item < n_items; item += gridDim.x, ++n_item) {
-            const int rest = item / nsplit;
+            int rest, part, parts;
+            decode(item, rest, part, parts);
+            (void)part;
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const int nkb = p.proj[proj].h_in / kBK;
@@ -294,7 +307,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         unsigned n2 = 0, nd = 0, n_item = 0;
         const bool bf16 = Cvt<T>::is_bf16;
         for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x, ++n_item) {
-            const int part = item % nsplit, rest = item / nsplit;
+            int rest, part, parts;
+            decode(item, rest, part, parts);
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
@@ -304,7 +318,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const unsigned sbo = 8u * t.rank * 2u;
             const unsigned idesc2 = make_idesc(bf16, kBM, kBN);
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
-            const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
+            const int nt0 = part * nnt_all / parts, nnt = (part + 1) * nnt_all / parts;
             for (int nt = nt0; nt < nnt; ++nt, ++n2, ++nd) {
                 const int s = n2 % kS2, buf = nd & 1;
                 mbar_wait(bar(FULL2 + s), (n2 / kS2) & 1, err, 16);
@@ -336,7 +350,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         const unsigned lane_base = (unsigned)(quad * 32) << 16;
         unsigned nd = 0, n_item = 0;
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
-            const int part = item % nsplit, rest = item / nsplit;
+            int rest, part, parts;
+            decode(item, rest, part, parts);
             const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
@@ -406,7 +421,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             }
             // ---- D2 slices -> y
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
-            const int nt0 = part * nnt_all / nsplit, nnt = (part + 1) * nnt_all / nsplit;
+            const int nt0 = part * nnt_all / parts, nnt = (part + 1) * nnt_all / parts;
             const bool live = row < t.valid;
             for (int nt = nt0; nt < nnt; ++nt, ++nd) {
                 const int buf = nd & 1;
