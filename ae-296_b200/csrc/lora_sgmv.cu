@@ -227,7 +227,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             int rest, part, parts;
             decode(item, rest, part, parts);
             (void)part;
-            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const int nkb = p.proj[proj].h_in / kBK;
             const int n_abox = t.rank / 8;
@@ -252,7 +252,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x) {
             int rest, part, parts;
             decode(item, rest, part, parts);
-            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
@@ -278,7 +278,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             int rest, part, parts;
             decode(item, rest, part, parts);
             (void)part;
-            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const int nkb = p.proj[proj].h_in / kBK;
             const int b1 = n_item & 1;
@@ -309,7 +309,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x, ++n_item) {
             int rest, part, parts;
             decode(item, rest, part, parts);
-            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             mbar_wait(bar(V_READY), n_item & 1, err, 15);
@@ -352,7 +352,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
             int rest, part, parts;
             decode(item, rest, part, parts);
-            const int proj = rest / n_tiles, tile = rest - proj * n_tiles;
+            const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
             const ProjArgs& pj = p.proj[proj];
             if (half != 0 && !do2) continue;
