@@ -144,3 +144,29 @@ def test_delta_then_add_mode(dtype):
     ulp = 2.0 ** (-10 if dtype == "fp16" else -7)
     assert np.abs(got - want).max() <= ulp * np.abs(want).max()
     assert (got != want).mean() < 0.02          # only ties of the delta's own rounding may differ
+
+
+@pytest.mark.parametrize("T,N,h_in,h_out,ranks,zipf,dtype", [
+    (256, 128, 4096, 4096, [8, 16, 32, 64], 1.0, "fp16"),      # decode batch of the 7B workload
+    (512, 96, 8192, 1024, 64, 1.2, "bf16"),                    # GQA k/v shapes of the 70B workload
+    (512, 96, 8192, 8192, 64, 1.2, "bf16"),                    # its q/o shapes: 64 units per segment
+])
+def test_full_size_decode_segments_spanning_many_ctas(T, N, h_in, h_out, ranks, zipf, dtype):
+    """At these sizes a work segment's units are spread over several CTAs, so its intermediate is
+    the sum of several split-K slots that the expand kernel's producers add up themselves."""
+    c = Case(T, N, h_in, h_out, ranks, dtype, seed=11, zipf=zipf, n_layers=1)
+    want = c.oracle_delta(0)
+    got32 = c.run(0, y_dtype=torch.float32)
+    assert rel_err(got32.double().cpu().numpy(), want) <= TOL
+    # 16-bit output: the single rounding of the fp32 result; a second run is bit-identical
+    got16 = c.run(0)
+    assert torch.equal(got16, got32.to(c.tdt))
+    assert torch.equal(c.run(0), got16)
+    # linearity in x: doubling x doubles the delta; exactly so in bf16 (powers of two commute with
+    # every rounding), up to the fp16 subnormals of the intermediate's lo halves in fp16
+    c.x = (c.x_cpu * 2).to(c.device)
+    twice = c.run(0, y_dtype=torch.float32)
+    if dtype == "bf16":
+        assert torch.equal(twice, got32 * 2)
+    else:
+        assert rel_err(twice.double().cpu().numpy(), 2 * got32.double().cpu().numpy()) <= 1e-5
