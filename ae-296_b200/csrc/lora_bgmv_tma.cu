@@ -400,30 +400,39 @@ __device__ __forceinline__ int shrink_chunks(const ApplyParams& p, int proj, int
     return (p.proj[proj].h_in + (1 << wshift) - 1) >> wshift;
 }
 
-// Adds up the slots of one segment for four consecutive rank indices of one token, ascending.
-template <typename T>
-__device__ __forceinline__ float4 fold_quad(const ApplyParams& p, const WorkspaceView& ws, size_t off, int seg_first,
-                                            int per_cta, int n_chunks) {
+// Adds up the slots of one segment, ascending, for NQ quads (four consecutive rank indices of
+// one token each) at once: the loads of all quads and of up to four slots are in flight together.
+template <typename T, int NQ>
+__device__ __forceinline__ void fold_quads(const ApplyParams& p, const WorkspaceView& ws, const size_t (&off)[NQ],
+                                           const bool (&on)[NQ], int seg_first, int per_cta, int n_chunks, float4 (&s)[NQ]) {
     const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) s[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     SlotWalk sw(seg_first, per_cta, n_chunks);
     while (sw.valid()) {
-        float4 v[4];
+        float4 v[4][NQ];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {                      // up to four loads in flight, summed in order
-            v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (sw.valid()) {
-                v[q] = __ldcg(reinterpret_cast<const float4*>(ws.partial + (size_t)sw.j * cstride + off));
-                sw.next(per_cta);
+        for (int q = 0; q < 4; ++q) {
+            const bool live = sw.valid();
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) {
+                v[q][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live && on[i]) v[q][i] = __ldcg(reinterpret_cast<const float4*>(ws.partial + (size_t)sw.j * cstride + off[i]));
             }
+            if (live) sw.next(per_cta);
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) { s.x += v[q].x; s.y += v[q].y; s.z += v[q].z; s.w += v[q].w; }
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) { s[i].x += v[q][i].x; s[i].y += v[q][i].y; s[i].z += v[q][i].z; s[i].w += v[q][i].w; }
     }
     if (p.flags & B200_LORA_MID_ROUND) {
-        s.x = Cvt<T>::round1(s.x); s.y = Cvt<T>::round1(s.y); s.z = Cvt<T>::round1(s.z); s.w = Cvt<T>::round1(s.w);
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            s[i].x = Cvt<T>::round1(s[i].x); s[i].y = Cvt<T>::round1(s[i].y);
+            s[i].z = Cvt<T>::round1(s[i].z); s[i].w = Cvt<T>::round1(s[i].w);
+        }
     }
-    return s;
 }
 
 template <typename T>
@@ -581,10 +590,24 @@ __device__ __forceinline__ void expand_produce(const ApplyParams& p, const Works
             const int seg_first = shrink_seg_first(p, fc.n_units, m.proj, u0);
             const int n_chunks = shrink_chunks(p, m.proj, r);
             const int qshift = 31 - __clz(r >> 2);             // quads of four rank indices per token
-            for (int idx = lane; idx < ((m.ntok * r) >> 2); idx += 32) {
-                const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
-                const size_t off = ((size_t)m.proj * p.cap + m.start + t) * kMaxRank + k4;
-                *reinterpret_cast<float4*>(vt + t * kVPitch + k4) = fold_quad<T>(p, ws, off, seg_first, fc.per_cta, n_chunks);
+            const int nq = (m.ntok * r) >> 2;
+            for (int base = 0; base < nq; base += 64) {        // two quads per lane and pass
+                size_t off[2];
+                bool on[2];
+                int dst[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int idx = base + 32 * i + lane;
+                    const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
+                    on[i] = idx < nq;
+                    off[i] = ((size_t)m.proj * p.cap + m.start + t) * kMaxRank + k4;
+                    dst[i] = t * kVPitch + k4;
+                }
+                float4 sum[2];
+                fold_quads<T, 2>(p, ws, off, on, seg_first, fc.per_cta, n_chunks, sum);
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    if (on[i]) *reinterpret_cast<float4*>(vt + dst[i]) = sum[i];
             }
         }
         __syncwarp();
@@ -900,7 +923,11 @@ __global__ void __launch_bounds__(128) fold_partials_kernel(const __grid_constan
         for (int idx = threadIdx.x; idx < ((ntok * r) >> 2); idx += blockDim.x) {
             const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
             const size_t off = ((size_t)proj * p.cap + start + t) * kMaxRank + k4;
-            *reinterpret_cast<float4*>(ws.v + off) = fold_quad<T>(p, ws, off, seg_first, per_cta, n_chunks);
+            const size_t offs[1] = {off};
+            const bool on[1] = {true};
+            float4 sum[1];
+            fold_quads<T, 1>(p, ws, offs, on, seg_first, per_cta, n_chunks, sum);
+            *reinterpret_cast<float4*>(ws.v + off) = sum[0];
         }
     }
 }
