@@ -401,8 +401,8 @@ __device__ __forceinline__ int shrink_chunks(const ApplyParams& p, int proj, int
 }
 
 // Adds up the slots of one segment, ascending, for NQ quads (four consecutive rank indices of
-// one token each) at once: the loads of all quads and of up to four slots are in flight together.
-template <typename T, int NQ>
+// one token each) at once: the loads of all quads and of up to NS slots are in flight together.
+template <typename T, int NQ, int NS = 4>
 __device__ __forceinline__ void fold_quads(const ApplyParams& p, const WorkspaceView& ws, const size_t (&off)[NQ],
                                            const bool (&on)[NQ], int seg_first, int per_cta, int n_chunks, float4 (&s)[NQ]) {
     const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
@@ -410,9 +410,9 @@ __device__ __forceinline__ void fold_quads(const ApplyParams& p, const Workspace
     for (int i = 0; i < NQ; ++i) s[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     SlotWalk sw(seg_first, per_cta, n_chunks);
     while (sw.valid()) {
-        float4 v[4][NQ];
+        float4 v[NS][NQ];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < NS; ++q) {
             const bool live = sw.valid();
 #pragma unroll
             for (int i = 0; i < NQ; ++i) {
@@ -422,7 +422,7 @@ __device__ __forceinline__ void fold_quads(const ApplyParams& p, const Workspace
             if (live) sw.next(per_cta);
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
+        for (int q = 0; q < NS; ++q)
 #pragma unroll
             for (int i = 0; i < NQ; ++i) { s[i].x += v[q][i].x; s[i].y += v[q][i].y; s[i].z += v[q][i].z; s[i].w += v[q][i].w; }
     }
@@ -861,13 +861,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             const Item it = make_item(p, rec, cur, true);
             // the CTA's first unit of a (projection, work segment) brings the intermediate along
             const bool need_v = n == 0 || (cur.sp == 0 && cur.sub == 0);
+            // ... except the CTA's very first unit, whose intermediate the (still idle) consumer
+            // warps add up with all their threads: it is on the kernel's critical path
+            const bool by_consumers = n == 0 && fc.n_units != 0;
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
             Meta* slot = &meta[n % kMetaSlots];
             publish_meta(slot, rec, it, lane);
-            if (lane == 0) { slot->pad[0] = need_v ? 1 : 0; slot->pad[1] = cur.unit; }
+            if (lane == 0) { slot->pad[0] = (need_v && !by_consumers) ? 1 : 0; slot->pad[1] = cur.unit; }
             __syncwarp();
+            if (n == 0) asm volatile("bar.arrive 2, %0;" ::"n"(kConsThreads + 32) : "memory");   // meta slot 0 is published
             const unsigned full = smem_u32(&bars[s]);
-            if (it.valid) expand_produce<T>(p, ws, it, rec, smem + s * kExpandStage, full, lane, waited ? 7 : 1, need_v, fc, cur.unit);
+            if (it.valid) expand_produce<T>(p, ws, it, rec, smem + s * kExpandStage, full, lane, waited ? 7 : 1, need_v && !by_consumers, fc, cur.unit);
             else if (lane == 0) mbar_arrive(full);
             if (n + kProdWarps < n_local) cursor_advance(p, n_units, true, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
@@ -875,6 +879,28 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         return;
     }
 
+    // The intermediate of the CTA's first unit: one quad per thread, up to eight slots in flight.
+    asm volatile("bar.sync 2, %0;" ::"n"(kConsThreads + 32) : "memory");       // producer 0 has published meta slot 0
+    if (!(p.flags & B200_LORA_ONLY_EXPAND)) {
+        const Meta m0 = load_meta(&meta[0]);
+        if (m0.valid) {
+            const int r = m0.u.rank;
+            const int per_a = (n_units * p.total_super_in + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int seg_first = shrink_seg_first(p, n_units, m0.proj, m0.pad[1]);
+            const int n_chunks = shrink_chunks(p, m0.proj, r);
+            const int qshift = 31 - __clz(r >> 2);
+            float* vt = reinterpret_cast<float*>(smem + kWTile + kYBytes);
+            for (int idx = tid; idx < ((m0.u.ntok * r) >> 2); idx += kConsThreads) {
+                const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
+                const size_t off[1] = {((size_t)m0.proj * p.cap + m0.u.start + t) * kMaxRank + k4};
+                const bool on[1] = {true};
+                float4 sum[1];
+                fold_quads<T, 1, 8>(p, ws, off, on, seg_first, per_a, n_chunks, sum);
+                *reinterpret_cast<float4*>(vt + t * kVPitch + k4) = sum[0];
+            }
+        }
+        cons_sync();
+    }
     unsigned bf[2][4][2];                                  // v fragments of the last (projection, work segment)
     int bf_key = -1;
     for (int n = 0; n < n_local; ++n) {
