@@ -64,6 +64,7 @@ struct PlanView {
     int* ws_start;      // [cap + 1]   work segments: adapter segments cut into <= kChunkTok tokens
     int* ws_adapter;    // [cap]
     int* ws_rank;       // [cap]
+    int* ws_unit0;      // [cap]       first unit record of the work segment
     int* unit_tab;      // [16 * cap][16]  one record per weight unit (see UnitRec)
     int* tile_tab;      // [cap]       two words per tile of a tall run: first sorted position, (seg << 8) | (rows - 1)
     int* hist;          // [n_adapters + 1]
@@ -72,7 +73,7 @@ struct PlanView {
 __host__ __device__ inline size_t plan_words(int cap, int n_adapters) {
     // header + perm + seg_start + 3 seg arrays + units + tiles + hist, each padded to 4 words
     auto pad4 = [](size_t w) { return (w + 3) & ~size_t(3); };
-    return 16 + pad4(cap) + 2 * pad4(cap + 1) + 5 * pad4(cap) + 16 * kMaxSub * (size_t)cap + pad4(cap) +
+    return 16 + pad4(cap) + 2 * pad4(cap + 1) + 6 * pad4(cap) + 16 * kMaxSub * (size_t)cap + pad4(cap) +
            pad4((size_t)n_adapters + 1);
 }
 
@@ -89,6 +90,7 @@ __host__ __device__ inline PlanView plan_view(void* base, int cap, int n_adapter
     v.ws_start = w;                                w += pad4(cap + 1);
     v.ws_adapter = w;                              w += pad4(cap);
     v.ws_rank = w;                                 w += pad4(cap);
+    v.ws_unit0 = w;                                w += pad4(cap);
     v.unit_tab = w;                                w += 16 * kMaxSub * (size_t)cap;
     v.tile_tab = w;                                w += pad4(cap);
     v.hist = w;

@@ -48,7 +48,7 @@ __device__ __forceinline__ int load_id(const void* ids, int t) {
 
 // Phase A (ids known): histogram, segment table, stable placement.
 template <typename IdT>
-__device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* smem) {
+__device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* smem, int* s_cur, int* s_perm) {
     const int tid = threadIdx.x;
     int* warp_sums = smem;              // 33 words
     int* s_bad = smem + 40;
@@ -79,13 +79,17 @@ __device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* 
                 pv.seg_adapter[seg_carry + sidx] = a;
             }
             pv.hist[a] = tok_carry + off;   // becomes the placement cursor
+            if (s_cur) s_cur[a] = tok_carry + off;
         }
         tok_carry += tot_c;
         seg_carry += tot_s;
     }
     if (tid == 0) { pv.seg_start[seg_carry] = T; pv.hdr->n_segs = seg_carry; pv.hdr->n_tokens = T; }
     __syncthreads();
-    // stable placement, one CTA-wide tile of tokens at a time, warps in order
+    // stable placement, one CTA-wide tile of tokens at a time, warps in order; the cursors live in
+    // shared memory when the adapter table fits (a global read-modify-write per warp and step
+    // would cost a memory round trip each)
+    int* cur = s_cur ? s_cur : pv.hist;
     const int lane = tid & 31, wid = tid >> 5;
     for (int base = 0; base < T; base += kPlanThreads) {
         int t = base + tid;
@@ -99,14 +103,20 @@ __device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* 
         int slot = 0;
         for (int w = 0; w < n_warps; ++w) {
             if (wid == w && valid && lane == leader) {
-                slot = pv.hist[a];
-                pv.hist[a] = slot + cnt;
+                slot = cur[a];
+                cur[a] = slot + cnt;
             }
             __syncthreads();
         }
         slot = __shfl_sync(0xffffffffu, slot, leader);
-        if (valid) pv.perm[slot + rank_in_warp] = t;
+        if (valid) {
+            pv.perm[slot + rank_in_warp] = t;
+            if (s_perm) s_perm[slot + rank_in_warp] = t;
+            if (slot + rank_in_warp != t) *s_bad = 2;          // some token moved: rows are not pre-grouped
+        }
     }
+    __syncthreads();
+    if (tid == 0 && *s_bad == 0) pv.hdr->identity = 1;     // sorted already: tall runs are whole segments
     __syncthreads();
 }
 
@@ -132,7 +142,7 @@ __device__ __forceinline__ void walk_segment(const int* perm, int b, int e, bool
 
 // Phase B: split segments into tall runs and short stretches, cut both into work segments of at
 // most kChunkTok tokens, lay out unit records (short ones first) and the tile list.
-__device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
+__device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem, const int* perm) {
     const int* ranks = ad.ranks;
     const long long* cum_ranks = ad.cum_ranks;
     const int r_pool = ad.r_pool;
@@ -160,7 +170,7 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
                 nsub = n_sub(pad_rank(r));
                 // tensor-core tiles take ranks 16/32/64 in a layout whose B rows are contiguous
                 tile_rank = (r == 16 || r == 32 || r == 64) && (cum_ranks || r == r_pool);
-                walk_segment(pv.perm, b, e, identity, tile_rank, [&](int kind, int pb, int pe) {
+                walk_segment(perm, b, e, identity, tile_rank, [&](int kind, int pb, int pe) {
                     const int ch = (pe - pb + kChunkTok - 1) / kChunkTok;
                     nchunk += ch;
                     if (kind) { ut += ch * nsub; nt += (pe - pb + kTileM - 1) / kTileM; }
@@ -177,27 +187,18 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
                 pv.seg_flags[s] = nt > 0 ? 1 : 0;
                 int u_short = c_short + o_s, u_tall = tot_short + c_tall + o_t;
                 int w = c_ws + o_w, tile = c_tiles + o_m;
-                const long long cum = cum_ranks ? cum_ranks[a] : 0;
-                const float scale = ad.scalings ? ad.scalings[a] : ad.scale;
-                walk_segment(pv.perm, b, e, identity, tile_rank, [&](int kind, int pb, int pe) {
+                // this thread lists the segment's work segments; their unit records are written
+                // afterwards by all threads, one work segment each
+                walk_segment(perm, b, e, identity, tile_rank, [&](int kind, int pb, int pe) {
                     const int len = pe - pb;
                     const int ch = (len + kChunkTok - 1) / kChunkTok;
                     const int per = (len + ch - 1) / ch;             // balanced chunk length
                     int& u = kind ? u_tall : u_short;
                     for (int c = 0; c < ch; ++c) {
-                        const int cb = pb + min(c * per, len), ce = pb + min((c + 1) * per, len);
-                        pv.ws_start[w] = cb;
+                        pv.ws_start[w] = pb + min(c * per, len);
                         pv.ws_adapter[w] = a;
                         pv.ws_rank[w] = r;
-                        UnitRec rec;
-                        rec.adapter = a; rec.rank = r; rec.ntok = (short)(ce - cb); rec.wseg = w; rec.start = cb;
-                        rec.scale = scale;
-                        rec.cum_lo = (int)(cum & 0xffffffffll); rec.cum_hi = (int)(cum >> 32);
-                        for (int i = 0; i < 8; ++i) rec.tok[i] = pv.perm[cb + min(i, ce - cb - 1)];
-                        for (int j = 0; j < nsub; ++j) {
-                            rec.sub = (short)j;
-                            reinterpret_cast<UnitRec*>(pv.unit_tab)[u + j] = rec;
-                        }
+                        pv.ws_unit0[w] = u;
                         u += nsub;
                         ++w;
                     }
@@ -221,11 +222,34 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem) {
         pv.hdr->n_units_short = tot_short;
         pv.hdr->n_tiles = tot_tiles;
     }
+    __syncthreads();
+    // unit records: one work segment per thread, n_sub records of four 16-byte stores each
+    for (int w = tid; w < tot_ws; w += kPlanThreads) {
+        const int cb = pv.ws_start[w], ce = pv.ws_start[w + 1];
+        const int a = pv.ws_adapter[w], r = pv.ws_rank[w];
+        const int nsub = n_sub(pad_rank(r));
+        const long long cum = cum_ranks ? cum_ranks[a] : 0;
+        UnitRec rec;
+        rec.adapter = a; rec.rank = r; rec.sub = 0; rec.ntok = (short)(ce - cb); rec.wseg = w; rec.start = cb;
+        rec.scale = ad.scalings ? ad.scalings[a] : ad.scale;
+        rec.cum_lo = (int)(cum & 0xffffffffll); rec.cum_hi = (int)(cum >> 32);
+        for (int i = 0; i < 8; ++i) rec.tok[i] = perm[cb + min(i, ce - cb - 1)];
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<UnitRec*>(pv.unit_tab) + pv.ws_unit0[w]);
+        for (int j = 0; j < nsub; ++j) {
+            rec.sub = (short)j;
+            const uint4* src = reinterpret_cast<const uint4*>(&rec);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[4 * j + q] = src[q];
+        }
+    }
 }
 
 template <typename IdT>
 __global__ void __launch_bounds__(kPlanThreads, 1)
-plan_build_kernel(void* plan, int cap, const void* ids, int T, const PlanAdapters ad) {
+plan_build_kernel(void* plan, int cap, const void* ids, int T, const PlanAdapters ad, int n_cur, int n_perm) {
+    extern __shared__ int dyn_smem[];                      // placement cursors [n_cur], then perm [n_perm]
+    int* s_cur = n_cur ? dyn_smem : nullptr;
+    int* s_perm = n_perm ? dyn_smem + n_cur : nullptr;
     const int N = ad.n_adapters;
     // no early launch of the successor here: the apply kernels read the plan before they wait
     // for their predecessor, which is safe only because a plan kernel has ended by then
@@ -237,10 +261,10 @@ plan_build_kernel(void* plan, int cap, const void* ids, int T, const PlanAdapter
         pv.hdr->n_units = 0; pv.hdr->n_tiles = 0; pv.hdr->n_units_short = 0; pv.hdr->n_segs = 0; pv.hdr->n_tokens = 0;
     }
     __syncthreads();
-    build_from_ids<IdT>(pv, ids, T, N, smem);
+    build_from_ids<IdT>(pv, ids, T, N, smem, s_cur, s_perm);
     __syncthreads();
     if (pv.hdr->error) return;
-    build_units(pv, ad, smem);
+    build_units(pv, ad, smem, s_perm ? s_perm : pv.perm);
 }
 
 __global__ void __launch_bounds__(kPlanThreads, 1)
@@ -273,15 +297,28 @@ plan_segments_kernel(void* plan, int cap, const int* seg_starts, const int* seg_
     for (int t = tid; t < T; t += kPlanThreads) pv.perm[t] = t;
     if (tid == 0) { pv.seg_start[S] = T; pv.hdr->n_segs = S; pv.hdr->n_tokens = T; }
     __syncthreads();
-    build_units(pv, ad, smem);
+    build_units(pv, ad, smem, pv.perm);
 }
 
 cudaError_t launch_plan_build(void* plan, int cap, const void* ids, int ids_i64, int n_tokens,
                               const PlanAdapters& ad, cudaStream_t s) {
+    // shared-memory copies of the placement cursors and of perm, when they fit
+    const int n_cur = (size_t)(ad.n_adapters + 1) * 4 <= 48 * 1024 ? ad.n_adapters + 1 : 0;
+    const int n_perm = (size_t)n_tokens * 4 <= 144 * 1024 ? n_tokens : 0;
+    const size_t smem = (size_t)(n_cur + n_perm) * 4;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(plan_build_kernel<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(plan_build_kernel<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
     if (ids_i64)
-        plan_build_kernel<long long><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ad);
+        plan_build_kernel<long long><<<1, kPlanThreads, smem, s>>>(plan, cap, ids, n_tokens, ad, n_cur, n_perm);
     else
-        plan_build_kernel<int><<<1, kPlanThreads, 0, s>>>(plan, cap, ids, n_tokens, ad);
+        plan_build_kernel<int><<<1, kPlanThreads, smem, s>>>(plan, cap, ids, n_tokens, ad, n_cur, n_perm);
     return cudaGetLastError();
 }
 
