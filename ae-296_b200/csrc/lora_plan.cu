@@ -53,12 +53,15 @@ __device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* 
     int* warp_sums = smem;              // 33 words
     int* s_bad = smem + 40;
     if (tid == 0) *s_bad = 0;
-    for (int a = tid; a <= N; a += kPlanThreads) pv.hist[a] = 0;
+    // histogram, in shared memory when the adapter table fits (hot adapters would serialise
+    // hundreds of global atomics on one address)
+    int* hist = s_cur ? s_cur : pv.hist;
+    for (int a = tid; a <= N; a += kPlanThreads) hist[a] = 0;
     __syncthreads();
     for (int t = tid; t < T; t += kPlanThreads) {
         int a = load_id<IdT>(ids, t);
         if (a < 0 || a >= N) *s_bad = 1;
-        else atomicAdd(&pv.hist[a], 1);
+        else atomicAdd(&hist[a], 1);
     }
     __syncthreads();
     if (*s_bad) {                        // leave an empty plan that applies nothing
@@ -69,7 +72,7 @@ __device__ void build_from_ids(PlanView pv, const void* ids, int T, int N, int* 
     int tok_carry = 0, seg_carry = 0;
     for (int base = 0; base < N; base += kPlanThreads) {
         int a = base + tid;
-        int c = a < N ? pv.hist[a] : 0;
+        int c = a < N ? hist[a] : 0;
         int tot_c, tot_s;
         int off = block_scan_excl(c, tot_c, warp_sums);
         int sidx = block_scan_excl(c > 0 ? 1 : 0, tot_s, warp_sums);
