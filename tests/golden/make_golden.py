@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path of the reference checkout>
 
 Two reference code paths run without a GPU and are executed UNMODIFIED here:
 
@@ -228,7 +228,7 @@ def bmm_case(ref_root, seed, B, L, H, rank, n_layers, layer):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     torch.manual_seed(0)
 
