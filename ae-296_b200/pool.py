@@ -89,6 +89,25 @@ class AdapterPool:
         self.a_block(a).copy_(A)
         self.b_block(a).copy_(B)
 
+    def load_adapter_async(self, a: int, A_host: torch.Tensor, B_host: torch.Tensor,
+                           stream: Optional["torch.cuda.Stream"] = None) -> "torch.cuda.Event":
+        """Host -> HBM copy of one adapter's weights into slot ``a`` on ``stream`` (a side stream,
+        so that the swap overlaps the running batch); returns the event the compute stream has to
+        wait for before the slot is used.  ``A_host [L, r, h_in]`` and ``B_host [L, h_out, r]``
+        should be pinned, otherwise the copies are synchronous.  The slot keeps its rank: a packed
+        pool cannot grow an adapter in place.  Counterpart of the reference's swapper copies
+        (csrc/cuda_ops.hpp:215-229 ``cudaHtoD2DAsyncLora``, lightllm/models/lora_gpu.py:298-321)."""
+        r = int(self.ranks_host[a])
+        if tuple(A_host.shape) != (self.n_layers, r, self.h_in) or tuple(B_host.shape) != (self.n_layers, self.h_out, r):
+            raise ValueError(f"slot {a} holds rank {r}: expected A [L,{r},{self.h_in}] and B [L,{self.h_out},{r}]")
+        stream = stream if stream is not None else torch.cuda.current_stream(self.wa.device)
+        with torch.cuda.stream(stream):
+            self.a_block(a).copy_(A_host, non_blocking=True)
+            self.b_block(a).copy_(B_host, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(stream)
+        return done
+
     def nbytes(self) -> int:
         return self.wa.numel() * self.wa.element_size() + self.wb.numel() * self.wb.element_size()
 

@@ -170,3 +170,25 @@ def test_full_size_decode_segments_spanning_many_ctas(T, N, h_in, h_out, ranks, 
         assert torch.equal(twice, got32 * 2)
     else:
         assert rel_err(twice.double().cpu().numpy(), 2 * got32.double().cpu().numpy()) <= 1e-5
+
+
+def test_adapter_swapped_in_on_a_side_stream():
+    """An adapter slot reloaded from pinned host memory on a side stream while the batch runs."""
+    c = Case(24, 6, 512, 768, [16, 32], "fp16", seed=21)
+    before = c.run(0, y_dtype=torch.float32)
+    a = int(c.ids[0])
+    g = torch.Generator().manual_seed(5)
+    r = int(c.ranks[a])
+    A_new = (torch.randn(c.n_layers, r, c.h_in, generator=g) / np.sqrt(c.h_in)).to(c.tdt).pin_memory()
+    B_new = (torch.randn(c.n_layers, c.h_out, r, generator=g) / np.sqrt(r)).to(c.tdt).pin_memory()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())          # the running batch still reads the slot
+    done = c.pool.load_adapter_async(a, A_new, B_new, side)
+    torch.cuda.current_stream().wait_event(done)
+    c.A[a], c.B[a] = A_new, B_new
+    after = c.run(0, y_dtype=torch.float32)
+    assert rel_err(after.double().cpu().numpy(), c.oracle_delta(0)) <= TOL
+    rows = torch.from_numpy(c.ids != a).cuda()
+    assert torch.equal(after[rows], before[rows])           # other adapters' tokens are untouched
+    with pytest.raises(ValueError):
+        c.pool.load_adapter_async(a, A_new[:, :8], B_new, side)
