@@ -116,3 +116,19 @@ def test_mixed_decode_and_prefill_from_ids():
     torch.cuda.synchronize()
     batch.workspace.check()
     assert rel_err(y.double().cpu().numpy(), c.oracle_delta(0)) <= TOL
+
+
+def test_full_size_prefill_batch():
+    """The prefill workload at full size (16 prompts of 128..1024 tokens, rank 32, hidden 4096): more
+    (tile, projection) pairs than CTAs, so the last round of pairs is cut by output columns."""
+    lens = [537, 824, 517, 341, 399, 247, 211, 845, 932, 822, 305, 334, 379, 996, 658, 989]
+    c = seg_case(lens, list(range(16)), [32] * 16, 16, 4096, 4096, "fp16", seed=2962)
+    want = c.oracle_delta(0)
+    y32 = run_segments(c, 0, y_dtype=torch.float32)
+    assert rel_err(y32.double().cpu().numpy(), want) <= TOL
+    y16 = run_segments(c, 0)
+    assert torch.equal(y16, y32.to(c.tdt))                 # one rounding of the fp32 result
+    assert torch.equal(run_segments(c, 0), y16)            # reproducible
+    # the reference's rounding of the intermediate (its prefill op keeps fp16 tensors)
+    y_mid = run_segments(c, 0, y_dtype=torch.float32, flags=L.MID_ROUND)
+    assert rel_err(y_mid.double().cpu().numpy(), c.oracle_delta(0, mid_round="fp16")) <= TOL
