@@ -265,6 +265,9 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
             ok = tensor_map_2d(&sp.xmap[i], q.x, (uint64_t)q.h_in, (uint64_t)n_tokens, 64, 128,
                                CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)q.ldx) &&
                  tensor_map_2d(&sp.amap[i], q.wa, (uint64_t)q.h_in, arows, 64, 8, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (ok && !p.y_f32)
+                ok = tensor_map_2d(&sp.ymap[i], q.y, (uint64_t)q.h_out, (uint64_t)n_tokens, 64, 128,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)q.ldy);
             for (int c = 0; c < 3 && ok; ++c) {
                 const uint64_t rc = 16u << c;
                 if (!adapters->packed && rc != (uint64_t)adapters->r_pool) continue;   // dense pools have one rank

@@ -175,6 +175,7 @@ struct SgmvParams {
     alignas(64) CUtensorMap xmap[kMaxProj];      // x [T, h_in], box 64 x 128, 128-byte swizzle
     CUtensorMap amap[kMaxProj];                  // A pool [rows, h_in], box 64 x 8, 128-byte swizzle
     CUtensorMap bmap[kMaxProj][3];               // B pool viewed as [rows, 16 | 32 | 64], box rank x 128
+    CUtensorMap ymap[kMaxProj];                  // y [T, h_out] (16-bit y only), box 64 x 128, 128-byte swizzle
 };
 
 // element offset of adapter a's A block [r, h] for `layer`, and its row count / row pitch

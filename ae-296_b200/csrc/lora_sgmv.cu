@@ -12,7 +12,9 @@
 // Warp roles: warps 0 and 3 issue TMA tensor copies (x and A boxes for phase 1, B boxes for
 // phase 2) into mbarrier-tracked rings; warp 1 allocates TMEM and has one thread issue the tcgen05.mma of
 // phase 1 into one of two D1 buffers, one item ahead; warp 2 has one thread issue those of phase
-// 2; both release ring slots and publish accumulators with tcgen05.commit; warps 4..11 read
+// 2 and moves y through shared memory (a [128, 128] block per slice comes in by tensor copy ahead of
+// its accumulator; blocks of whole tiles leave by tensor store, rows of a run's last, partial tile are
+// stored by their threads); both MMA warps release ring slots and publish accumulators with tcgen05.commit; warps 4..11 read
 // accumulators with tcgen05.ld (each warp its own 32-lane quadrant of TMEM, two warps per
 // quadrant sharing a slice's columns) and do the conversion and the y update.  Operand tiles use the 128/64/32-byte swizzled K-major layouts
 // that TMA writes and the MMA descriptors name.  Two D2 buffers let the MMA of slice n+1 overlap
@@ -40,8 +42,10 @@ constexpr int kATile = 64 * kBK * 2;             // 8 KB (rank 64)
 constexpr int kStage1 = kXTile + kATile;
 constexpr int kBTile = kBN * 64 * 2;             // 16 KB (rank 64)
 constexpr int kVTile = kBM * 64 * 2;             // 16 KB
-constexpr int kSmemTiles = kS1 * kStage1 + kS2 * kBTile + 2 * kVTile;
-constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 6 + 4;
+constexpr int kYS = 2;               // y staging slots (16-bit y)
+constexpr int kYTile = kBM * kBN * 2;            // 32 KB: two boxes of 64 columns, 128-byte swizzled rows
+constexpr int kSmemTiles = kS1 * kStage1 + kS2 * kBTile + 2 * kVTile + kYS * kYTile;
+constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 6 + 4 + 2 * kYS;
 constexpr int kSgmvSmem = kSmemTiles + kNumBars * 8 + 64 + 1024;     // + alignment slack
 constexpr int kEpiWarps = 8;         // two per TMEM lane quadrant: each takes half the columns of a slice
 constexpr int kSgmvThreads = 128 + kEpiWarps * 32;   // phase-1 TMA, phase-1 MMA, phase-2 MMA, phase-2 TMA, epilogue
@@ -78,6 +82,14 @@ __device__ __forceinline__ void tensor_g2s_2d(unsigned dst, const void* tmap, in
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tensor_s2g_2d(const void* tmap, int x, int y, unsigned src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(tmap), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the committed stores have read their shared-memory source / have completed
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ---- tcgen05 wrappers -----------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(unsigned smem_dst, unsigned ncols) {
@@ -166,12 +178,13 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     unsigned char* stage2 = smem + kS1 * kStage1;
     unsigned char* vhi = stage2 + kS2 * kBTile;
     unsigned char* vlo = vhi + kVTile;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(vlo + kVTile);
+    unsigned char* ystage = vlo + kVTile;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(ystage + kYS * kYTile);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + kNumBars);
     // barrier indices
     const int FULL1 = 0, EMPTY1 = kS1, FULL2 = 2 * kS1, EMPTY2 = 2 * kS1 + kS2;
     const int D1_FULL = 2 * kS1 + 2 * kS2, D1_EMPTY = D1_FULL + 2, V_READY = D1_FULL + 4, V_FREE = D1_FULL + 5;
-    const int D2_FULL = D1_FULL + 6, D2_EMPTY = D1_FULL + 8;
+    const int D2_FULL = D1_FULL + 6, D2_EMPTY = D1_FULL + 8, Y_FULL = D1_FULL + 10, Y_DONE = Y_FULL + kYS;
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
     pdl_wait_prior();
@@ -201,6 +214,9 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
     // tensor-parallel callers run the two halves separately and sum v in between
     const bool do1 = !(p.flags & B200_LORA_ONLY_EXPAND), do2 = !(p.flags & B200_LORA_ONLY_SHRINK);
+    // 16-bit y goes through shared memory: tensor copies bring a slice's [128, 128] block in ahead
+    // of its accumulator and, for tiles whose 128 rows all belong to the run, carry the sum back
+    const bool y_staged = !p.y_f32;
 
     if (tid == 0) {
         for (int s = 0; s < kS1; ++s) { mbar_init(bar(FULL1 + s), 1); mbar_init(bar(EMPTY1 + s), 1); }
@@ -209,6 +225,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         mbar_init(bar(V_READY), 128);
         mbar_init(bar(V_FREE), 1);
         for (int b = 0; b < 2; ++b) { mbar_init(bar(D2_FULL + b), 1); mbar_init(bar(D2_EMPTY + b), kEpiWarps * 32); }
+        for (int b = 0; b < kYS; ++b) { mbar_init(bar(Y_FULL + b), 1); mbar_init(bar(Y_DONE + b), kEpiWarps * 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                    // one warp owns the TMEM allocation
@@ -248,7 +265,23 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     } else if (warp == 3) {
         // ================= TMA producer, phase 2: B boxes =================
         // (a warp of its own: phase 1 runs an item ahead and must not queue behind these copies)
-        unsigned n2 = 0;
+        // It also moves y: the load of slice n goes out as soon as the epilogue has finished with
+        // slice n - kYS, whose slot it takes over after that slice's store has read the slot.
+        unsigned n2 = 0, ny = 0;
+        int st_proj0 = 0, st_col0 = 0, st_row0 = 0, st_proj1 = 0, st_col1 = 0, st_row1 = 0;   // st_proj < 0: nothing to store
+        auto retire = [&](unsigned k) {                       // slice k of this CTA
+            const int ys = k % kYS;
+            mbar_wait(bar(Y_DONE + ys), (k / kYS) & 1, err, 21);
+            const int sp_ = ys ? st_proj1 : st_proj0, sc = ys ? st_col1 : st_col0, sr = ys ? st_row1 : st_row0;
+            if (lane == 0 && sp_ >= 0) {
+                const unsigned src = smem_u32(ystage + ys * kYTile);
+                tensor_s2g_2d(&sp.ymap[sp_], sc, sr, src);
+                if (sc + 64 < p.proj[sp_].h_out) tensor_s2g_2d(&sp.ymap[sp_], sc + 64, sr, src + kYTile / 2);
+                bulk_commit();
+                bulk_wait_read();
+            }
+            __syncwarp();
+        };
         for (int item = blockIdx.x; do2 && item < n_items; item += gridDim.x) {
             int rest, part, parts;
             decode(item, rest, part, parts);
@@ -266,8 +299,26 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                                   bar(FULL2 + s));
                 }
                 __syncwarp();
+                if (y_staged) {
+                    static_assert(kYS == 2, "two slots of store bookkeeping");
+                    const int ys = ny % kYS;
+                    if (ny >= (unsigned)kYS) retire(ny - kYS);
+                    if (lane == 0) {
+                        const unsigned dst = smem_u32(ystage + ys * kYTile);
+                        mbar_arrive_expect_tx(bar(Y_FULL + ys), kYTile);
+                        tensor_g2s_2d(dst, &sp.ymap[proj], nt * kBN, t.row0, bar(Y_FULL + ys));
+                        tensor_g2s_2d(dst + kYTile / 2, &sp.ymap[proj], nt * kBN + 64, t.row0, bar(Y_FULL + ys));
+                    }
+                    __syncwarp();
+                    const int keep = t.valid == kBM ? proj : -1;      // other tiles are stored row by row by the epilogue
+                    if (ys) { st_proj1 = keep; st_col1 = nt * kBN; st_row1 = t.row0; }
+                    else    { st_proj0 = keep; st_col0 = nt * kBN; st_row0 = t.row0; }
+                    ++ny;
+                }
             }
         }
+        for (unsigned k = ny > (unsigned)kYS ? ny - kYS : 0u; k < ny; ++k) retire(k);
+        if (lane == 0) bulk_wait_all();
     } else if (warp == 1) {
         // ================= MMA issuer, phase 1: D1[item & 1] = X . A^T =================
         // runs one item ahead of phase 2, so the x stream of the next item overlaps the y update
@@ -422,19 +473,14 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             // ---- D2 slices -> y
             const int nnt_all = (pj.h_out + kBN - 1) / kBN;
             const int nt0 = part * nnt_all / parts, nnt = (part + 1) * nnt_all / parts;
-            const bool live = row < t.valid;
+            const bool live = row < t.valid, whole = t.valid == kBM;
             for (int nt = nt0; nt < nnt; ++nt, ++nd) {
-                const int buf = nd & 1;
-                // the y slice of this row does not depend on the MMA: fetch all of it first, so
-                // sixteen loads are in flight while the accumulator is being produced
-                uint4 yv[kBN / 16];
-                const bool pre = live && !p.y_f32;
+                const int buf = nd & 1, ys = nd % kYS;
+                // this thread's 128 bytes of the staged y block: row `row` of the box of its column half;
+                // the 16-byte chunk c of a row sits at chunk c ^ (row & 7)
+                unsigned char* ysm = ystage + ys * kYTile + half * (kYTile / 2) + row * 128;
                 uint4* yrow = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)(t.row0 + row) * pj.ldy + nt * kBN) + half * (kBN / 16);
-                if (pre) {
-#pragma unroll
-                    for (int q = 0; q < kBN / 16; ++q)
-                        if (nt * kBN + half * (kBN / 2) + q * 8 < pj.h_out) yv[q] = yrow[q];
-                }
+                if (y_staged) mbar_wait(bar(Y_FULL + ys), (nd / kYS) & 1, err, 22);
                 mbar_wait(bar(D2_FULL + buf), (nd >> 1) & 1, err, 20);
                 tc_fence_after();
 #pragma unroll
@@ -442,8 +488,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                     float v[16];
                     tc_ld16(tmem + lane_base + kD2Col + buf * kBN + half * (kBN / 2) + c * 16, v);
                     const int col = nt * kBN + half * (kBN / 2) + c * 16;
-                    if (live && col < pj.h_out) {
-                        if (p.y_f32) {
+                    if (p.y_f32) {
+                        if (live && col < pj.h_out) {
                             float4* yp = reinterpret_cast<float4*>(reinterpret_cast<float*>(pj.y) +
                                                                    (long long)(t.row0 + row) * pj.ldy + col);
 #pragma unroll
@@ -453,20 +499,26 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                                 y4.z += t.scale * v[4 * q + 2]; y4.w += t.scale * v[4 * q + 3];
                                 yp[q] = y4;
                             }
-                        } else {
+                        }
+                    } else {
 #pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                uint4 y4 = yv[2 * c + q];
-                                float f[8];
-                                Cvt<T>::unpack8(y4, f);
-                                y4.x = Cvt<T>::pack2(f[0] + t.scale * v[8 * q], f[1] + t.scale * v[8 * q + 1]);
-                                y4.y = Cvt<T>::pack2(f[2] + t.scale * v[8 * q + 2], f[3] + t.scale * v[8 * q + 3]);
-                                y4.z = Cvt<T>::pack2(f[4] + t.scale * v[8 * q + 4], f[5] + t.scale * v[8 * q + 5]);
-                                y4.w = Cvt<T>::pack2(f[6] + t.scale * v[8 * q + 6], f[7] + t.scale * v[8 * q + 7]);
-                                yrow[2 * c + q] = y4;
-                            }
+                        for (int q = 0; q < 2; ++q) {
+                            uint4* ys4 = reinterpret_cast<uint4*>(ysm + (((2 * c + q) ^ (row & 7)) << 4));
+                            uint4 y4 = *ys4;
+                            float f[8];
+                            Cvt<T>::unpack8(y4, f);
+                            y4.x = Cvt<T>::pack2(f[0] + t.scale * v[8 * q], f[1] + t.scale * v[8 * q + 1]);
+                            y4.y = Cvt<T>::pack2(f[2] + t.scale * v[8 * q + 2], f[3] + t.scale * v[8 * q + 3]);
+                            y4.z = Cvt<T>::pack2(f[4] + t.scale * v[8 * q + 4], f[5] + t.scale * v[8 * q + 5]);
+                            y4.w = Cvt<T>::pack2(f[6] + t.scale * v[8 * q + 6], f[7] + t.scale * v[8 * q + 7]);
+                            if (whole) *ys4 = y4;                                   // leaves with the slot's tensor store
+                            else if (live && col < pj.h_out) yrow[2 * c + q] = y4;
                         }
                     }
+                }
+                if (y_staged) {
+                    if (whole) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor store
+                    mbar_arrive(bar(Y_DONE + ys));
                 }
                 tc_fence_before();
                 mbar_arrive(bar(D2_EMPTY + buf));
