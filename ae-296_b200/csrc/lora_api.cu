@@ -248,6 +248,7 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     p.flags = flags;
     p.y_f32 = (y_dtype == B200_LORA_F32);
     p.cap = max_tokens;
+    p.n_tokens = n_tokens;
     p.plan = const_cast<void*>(plan);
     p.workspace = workspace;
 
@@ -263,8 +264,7 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
         for (int i = 0; i < n_proj && ok; ++i) {
             const b200_lora_proj& q = projs[i];
             ok = tensor_map_2d(&sp.xmap[i], q.x, (uint64_t)q.h_in, (uint64_t)n_tokens, 64, 128,
-                               CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)q.ldx) &&
-                 tensor_map_2d(&sp.amap[i], q.wa, (uint64_t)q.h_in, arows, 64, 8, CU_TENSOR_MAP_SWIZZLE_128B);
+                               CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)q.ldx);
             if (ok && !p.y_f32)
                 ok = tensor_map_2d(&sp.ymap[i], q.y, (uint64_t)q.h_out, (uint64_t)n_tokens, 64, 128,
                                    CU_TENSOR_MAP_SWIZZLE_128B, (uint64_t)q.ldy);
@@ -274,7 +274,8 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
                 const uint64_t brows = arows * (uint64_t)q.h_out / rc;
                 const CUtensorMapSwizzle sw = c == 0 ? CU_TENSOR_MAP_SWIZZLE_32B
                                             : c == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
-                ok = tensor_map_2d(&sp.bmap[i][c], q.wb, rc, brows, (uint32_t)rc, 128, sw);
+                ok = tensor_map_2d(&sp.bmap[i][c], q.wb, rc, brows, (uint32_t)rc, 128, sw) &&
+                     tensor_map_2d(&sp.amap[i][c], q.wa, (uint64_t)q.h_in, arows, 64, (uint32_t)rc, CU_TENSOR_MAP_SWIZZLE_128B);
             }
         }
         if (!ok) p.flags |= B200_LORA_NO_TENSOR;        // no driver entry point: everything on the BGMV kernels

@@ -166,6 +166,7 @@ struct ApplyParams {
     int flags;
     int y_f32;
     int cap;
+    int n_tokens;                        // rows of x and y in this call (<= cap)
     void* plan;
     void* workspace;
 };
@@ -173,7 +174,7 @@ struct ApplyParams {
 // Tensor maps of the tcgen05 tile kernel (all over local memory).
 struct SgmvParams {
     alignas(64) CUtensorMap xmap[kMaxProj];      // x [T, h_in], box 64 x 128, 128-byte swizzle
-    CUtensorMap amap[kMaxProj];                  // A pool [rows, h_in], box 64 x 8, 128-byte swizzle
+    CUtensorMap amap[kMaxProj][3];               // A pool [rows, h_in], box 64 x (16 | 32 | 64), 128-byte swizzle
     CUtensorMap bmap[kMaxProj][3];               // B pool viewed as [rows, 16 | 32 | 64], box rank x 128
     CUtensorMap ymap[kMaxProj];                  // y [T, h_out] (16-bit y only), box 64 x 128, 128-byte swizzle
 };

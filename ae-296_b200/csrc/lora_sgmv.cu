@@ -35,23 +35,36 @@ namespace {
 constexpr int kBM = 128;            // token rows per tile
 constexpr int kBK = 64;             // k columns per phase-1 block (one 128-byte swizzle atom)
 constexpr int kBN = 128;            // output columns per phase-2 slice
-constexpr int kS1 = 4;              // phase-1 ring slots
+constexpr int kS1 = 4;              // phase-1 ring slots (deeper rings measured no faster: one SM's copy
+                                    // engine sustains about 50 GB/s whatever is in flight)
 constexpr int kS2 = 2;              // phase-2 ring slots
 constexpr int kXTile = kBM * kBK * 2;            // 16 KB
 constexpr int kATile = 64 * kBK * 2;             // 8 KB (rank 64)
 constexpr int kStage1 = kXTile + kATile;
 constexpr int kBTile = kBN * 64 * 2;             // 16 KB (rank 64)
 constexpr int kVTile = kBM * 64 * 2;             // 16 KB
-constexpr int kYS = 2;               // y staging slots (16-bit y)
+constexpr int kYS = 2;               // y staging slots (16-bit y) when both phases run in one launch
+constexpr int kYSMax = 4;            // ... when a launch runs phase 2 only (they take the phase-1 ring's room)
 constexpr int kYTile = kBM * kBN * 2;            // 32 KB: two boxes of 64 columns, 128-byte swizzled rows
 constexpr int kSmemTiles = kS1 * kStage1 + kS2 * kBTile + 2 * kVTile + kYS * kYTile;
-constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 6 + 4 + 2 * kYS;
-constexpr int kSgmvSmem = kSmemTiles + kNumBars * 8 + 64 + 1024;     // + alignment slack
+constexpr int kNumBars = 2 * kS1 + 2 * kS2 + 6 + 4 + 2 * kYSMax;
+static_assert(kS1 * kStage1 + kYS * kYTile >= kYSMax * kYTile, "the y slots of a phase-2 launch fit the ring's room");
+static_assert((kYS & (kYS - 1)) == 0 && (kYSMax & (kYSMax - 1)) == 0, "slot counts are powers of two");
+constexpr int kSgmvSmem = kSmemTiles + kNumBars * 8 + 128 + 1024;    // + TMEM address and y slot state + alignment slack
 constexpr int kEpiWarps = 8;         // two per TMEM lane quadrant: each takes half the columns of a slice
 constexpr int kSgmvThreads = 128 + kEpiWarps * 32;   // phase-1 TMA, phase-1 MMA, phase-2 MMA, phase-2 TMA, epilogue
 constexpr int kTmemCols = 512;
 constexpr int kD1Col = 0, kD2Col = 128;     // two D1 buffers of 64 columns, two D2 buffers of 128
 constexpr unsigned kSpinLimit = 1u << 22;
+// Launcher-internal flag (above the public bits): the two launches of a batch with few tiles.  The
+// phase-1 launch cuts every (tile, projection) pair along k, one CTA per part; the parts' fp32 sums
+// go to the split-K partial buffers and the last CTA to finish a pair adds them, in part order, into v.
+constexpr int kFlagKSplit = 1 << 16;
+constexpr int kMaxKSplit = 8;
+// Launcher-internal: the phase-2 launch that follows it.  It is launched with programmatic stream
+// serialization and waits for the phase-1 launch only where it reads v; its set-up and its first
+// B and y copies (nothing the phase-1 launch writes) overlap that launch's tail.
+constexpr int kFlagLateWait = 1 << 17;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -174,20 +187,29 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* stage1 = smem;
-    unsigned char* stage2 = smem + kS1 * kStage1;
+    // tensor-parallel callers, and the launcher when tiles are few, run the two halves separately
+    const bool do1 = !(p.flags & B200_LORA_ONLY_EXPAND), do2 = !(p.flags & B200_LORA_ONLY_SHRINK);
+    // Shared memory: B ring, V (hi, lo), then the phase-1 ring followed by the y slots.  A launch
+    // of phase 2 only has more y slots, in the ring's room.
+    constexpr int ns1 = kS1;
+    const int nys = !do1 ? kYSMax : kYS, nys_log = !do1 ? 2 : 1;
+    unsigned char* stage2 = smem;
     unsigned char* vhi = stage2 + kS2 * kBTile;
     unsigned char* vlo = vhi + kVTile;
-    unsigned char* ystage = vlo + kVTile;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(ystage + kYS * kYTile);
+    unsigned char* flex = vlo + kVTile;
+    unsigned char* stage1 = flex;
+    unsigned char* ystage = !do1 ? flex : flex + kS1 * kStage1;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + kSmemTiles);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + kNumBars);
+    int* ystate = reinterpret_cast<int*>(tmem_slot + 1);        // per y slot: projection (< 0: no store), column, row
+    int* last_flag = ystate + 3 * kYSMax;                       // k-split phase 1: this CTA adds the pair's parts
     // barrier indices
     const int FULL1 = 0, EMPTY1 = kS1, FULL2 = 2 * kS1, EMPTY2 = 2 * kS1 + kS2;
     const int D1_FULL = 2 * kS1 + 2 * kS2, D1_EMPTY = D1_FULL + 2, V_READY = D1_FULL + 4, V_FREE = D1_FULL + 5;
-    const int D2_FULL = D1_FULL + 6, D2_EMPTY = D1_FULL + 8, Y_FULL = D1_FULL + 10, Y_DONE = Y_FULL + kYS;
+    const int D2_FULL = D1_FULL + 6, D2_EMPTY = D1_FULL + 8, Y_FULL = D1_FULL + 10, Y_DONE = Y_FULL + kYSMax;
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
-    pdl_wait_prior();
+    if (!(p.flags & kFlagLateWait)) pdl_wait_prior();
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
@@ -201,19 +223,27 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const int base_items = n_tiles * p.n_proj;
     const int n_cta = (int)gridDim.x;
     const int n_full = (base_items / n_cta) * n_cta, n_rem = base_items - n_full;
+    // k parts per pair of a phase-1 launch with few pairs (both launches compute the same number)
+    // (bounded by the k blocks of the narrowest input and by the partial buffers the workspace holds)
+    int ksplit = ((p.flags & kFlagKSplit) && base_items > 0) ? max(1, min(kMaxKSplit, n_cta / base_items)) : 1;
+    {
+        int h_min = p.proj[0].h_in, h_max = p.proj[0].h_in;
+        for (int i = 1; i < p.n_proj; ++i) { h_min = min(h_min, p.proj[i].h_in); h_max = max(h_max, p.proj[i].h_in); }
+        ksplit = max(1, min(ksplit, min(h_min / kBK, max_kchunks(h_max))));
+    }
+    const bool k_items = ksplit > 1 && (p.flags & B200_LORA_ONLY_SHRINK);
     int nsplit = 1;
     if (n_rem > 0 && !(p.flags & B200_LORA_ONLY_SHRINK)) nsplit = min(8, max(1, (2 * n_cta) / n_rem));
     for (int i = 0; i < p.n_proj; ++i)                    // every part must own at least one column slice
         nsplit = min(nsplit, (p.proj[i].h_out + kBN - 1) / kBN);
-    const int n_items = n_full + n_rem * nsplit;
-    // item -> pair, part, parts of the pair
+    const int n_items = k_items ? base_items * ksplit : n_full + n_rem * nsplit;
+    // item -> pair, part, parts of the pair (parts of k in a k-split phase-1 launch, else of the output columns)
     auto decode = [&](int item, int& rest, int& part, int& parts) {
-        if (item < n_full) { rest = item; part = 0; parts = 1; }
+        if (k_items) { rest = item / ksplit; part = item - rest * ksplit; parts = ksplit; }
+        else if (item < n_full) { rest = item; part = 0; parts = 1; }
         else { const int j = item - n_full; rest = n_full + j / nsplit; part = j % nsplit; parts = nsplit; }
     };
     const bool mid_round = (p.flags & B200_LORA_MID_ROUND) != 0;
-    // tensor-parallel callers run the two halves separately and sum v in between
-    const bool do1 = !(p.flags & B200_LORA_ONLY_EXPAND), do2 = !(p.flags & B200_LORA_ONLY_SHRINK);
     // 16-bit y goes through shared memory: tensor copies bring a slice's [128, 128] block in ahead
     // of its accumulator and, for tiles whose 128 rows all belong to the run, carry the sum back
     const bool y_staged = !p.y_f32;
@@ -225,7 +255,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         mbar_init(bar(V_READY), 128);
         mbar_init(bar(V_FREE), 1);
         for (int b = 0; b < 2; ++b) { mbar_init(bar(D2_FULL + b), 1); mbar_init(bar(D2_EMPTY + b), kEpiWarps * 32); }
-        for (int b = 0; b < kYS; ++b) { mbar_init(bar(Y_FULL + b), 1); mbar_init(bar(Y_DONE + b), kEpiWarps * 32); }
+        for (int b = 0; b < kYSMax; ++b) { mbar_init(bar(Y_FULL + b), 1); mbar_init(bar(Y_DONE + b), kEpiWarps * 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                    // one warp owns the TMEM allocation
@@ -243,37 +273,35 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         for (int item = blockIdx.x; do1 && item < n_items; item += gridDim.x) {
             int rest, part, parts;
             decode(item, rest, part, parts);
-            (void)part;
             const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
-            const int nkb = p.proj[proj].h_in / kBK;
-            const int n_abox = t.rank / 8;
-            for (int kb = 0; kb < nkb; ++kb, ++n1) {
-                const int s = n1 % kS1;
-                mbar_wait(bar(EMPTY1 + s), ((n1 / kS1) & 1) ^ 1, err, 11);
+            const int nkb_all = p.proj[proj].h_in / kBK;
+            const int kb0 = k_items ? part * nkb_all / parts : 0, kb1 = k_items ? (part + 1) * nkb_all / parts : nkb_all;
+            for (int kb = kb0; kb < kb1; ++kb, ++n1) {
+                const int s = n1 % ns1;
+                mbar_wait(bar(EMPTY1 + s), ((n1 / ns1) & 1) ^ 1, err, 11);
                 const unsigned dst = smem_u32(stage1 + s * kStage1);
                 if (lane == 0) mbar_arrive_expect_tx(bar(FULL1 + s), kXTile + t.rank * kBK * 2);
                 __syncwarp();
-                // one instruction: lane 8 the x box [64 x 128], lanes 0..7 the A boxes [64 x 8]
-                if (lane == 8)
+                // two copies per block (the copy count, not the byte count, is what this kernel is short
+                // of): lane 1 the x box [64 x 128], lane 0 the A box [64 x rank]
+                if (lane == 1)
                     tensor_g2s_2d(dst, &sp.xmap[proj], kb * kBK, t.row0, bar(FULL1 + s));
-                else if (lane < n_abox)
-                    tensor_g2s_2d(dst + kXTile + lane * 1024, &sp.amap[proj], kb * kBK, (int)t.a_row0 + lane * 8,
-                                  bar(FULL1 + s));
+                else if (lane == 0)
+                    tensor_g2s_2d(dst + kXTile, &sp.amap[proj][t.cls], kb * kBK, (int)t.a_row0, bar(FULL1 + s));
             }
         }
     } else if (warp == 3) {
         // ================= TMA producer, phase 2: B boxes =================
         // (a warp of its own: phase 1 runs an item ahead and must not queue behind these copies)
         // It also moves y: the load of slice n goes out as soon as the epilogue has finished with
-        // slice n - kYS, whose slot it takes over after that slice's store has read the slot.
+        // the slice that used the slot before, and after that slice's store has read the slot.
         unsigned n2 = 0, ny = 0;
-        int st_proj0 = 0, st_col0 = 0, st_row0 = 0, st_proj1 = 0, st_col1 = 0, st_row1 = 0;   // st_proj < 0: nothing to store
         auto retire = [&](unsigned k) {                       // slice k of this CTA
-            const int ys = k % kYS;
-            mbar_wait(bar(Y_DONE + ys), (k / kYS) & 1, err, 21);
-            const int sp_ = ys ? st_proj1 : st_proj0, sc = ys ? st_col1 : st_col0, sr = ys ? st_row1 : st_row0;
-            if (lane == 0 && sp_ >= 0) {
+            const int ys = k & (nys - 1);
+            mbar_wait(bar(Y_DONE + ys), (k >> nys_log) & 1, err, 21);
+            if (lane == 0 && ystate[3 * ys] >= 0) {
+                const int sp_ = ystate[3 * ys], sc = ystate[3 * ys + 1], sr = ystate[3 * ys + 2];
                 const unsigned src = smem_u32(ystage + ys * kYTile);
                 tensor_s2g_2d(&sp.ymap[sp_], sc, sr, src);
                 if (sc + 64 < p.proj[sp_].h_out) tensor_s2g_2d(&sp.ymap[sp_], sc + 64, sr, src + kYTile / 2);
@@ -300,24 +328,23 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                 }
                 __syncwarp();
                 if (y_staged) {
-                    static_assert(kYS == 2, "two slots of store bookkeeping");
-                    const int ys = ny % kYS;
-                    if (ny >= (unsigned)kYS) retire(ny - kYS);
+                    const int ys = ny & (nys - 1);
+                    if (ny >= (unsigned)nys) retire(ny - nys);
                     if (lane == 0) {
                         const unsigned dst = smem_u32(ystage + ys * kYTile);
                         mbar_arrive_expect_tx(bar(Y_FULL + ys), kYTile);
                         tensor_g2s_2d(dst, &sp.ymap[proj], nt * kBN, t.row0, bar(Y_FULL + ys));
                         tensor_g2s_2d(dst + kYTile / 2, &sp.ymap[proj], nt * kBN + 64, t.row0, bar(Y_FULL + ys));
+                        ystate[3 * ys] = t.valid == kBM ? proj : -1;      // other tiles are stored row by row by the epilogue
+                        ystate[3 * ys + 1] = nt * kBN;
+                        ystate[3 * ys + 2] = t.row0;
                     }
                     __syncwarp();
-                    const int keep = t.valid == kBM ? proj : -1;      // other tiles are stored row by row by the epilogue
-                    if (ys) { st_proj1 = keep; st_col1 = nt * kBN; st_row1 = t.row0; }
-                    else    { st_proj0 = keep; st_col0 = nt * kBN; st_row0 = t.row0; }
                     ++ny;
                 }
             }
         }
-        for (unsigned k = ny > (unsigned)kYS ? ny - kYS : 0u; k < ny; ++k) retire(k);
+        for (unsigned k = ny > (unsigned)nys ? ny - nys : 0u; k < ny; ++k) retire(k);
         if (lane == 0) bulk_wait_all();
     } else if (warp == 1) {
         // ================= MMA issuer, phase 1: D1[item & 1] = X . A^T =================
@@ -328,27 +355,27 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         for (int item = blockIdx.x; do1 && item < n_items; item += gridDim.x, ++n_item) {
             int rest, part, parts;
             decode(item, rest, part, parts);
-            (void)part;
             const int tile = rest / p.n_proj, proj = rest - tile * p.n_proj;   // a tile's projections are neighbours: x is read from DRAM once
             const TileInfo t = tile_info(sp, p, pv, tile, proj);
-            const int nkb = p.proj[proj].h_in / kBK;
+            const int nkb_all = p.proj[proj].h_in / kBK;
+            const int kb0 = k_items ? part * nkb_all / parts : 0, kb1 = k_items ? (part + 1) * nkb_all / parts : nkb_all;
             const int b1 = n_item & 1;
             // the buffer must have been drained by the epilogue of the item two before
             mbar_wait(bar(D1_EMPTY + b1), ((n_item >> 1) & 1) ^ 1, err, 13);
             tc_fence_after();
             const unsigned idesc1 = make_idesc(bf16, kBM, t.rank);
-            for (int kb = 0; kb < nkb; ++kb, ++n1) {
-                const int s = n1 % kS1;
-                mbar_wait(bar(FULL1 + s), (n1 / kS1) & 1, err, 14);
+            for (int kb = kb0; kb < kb1; ++kb, ++n1) {
+                const int s = n1 % ns1;
+                mbar_wait(bar(FULL1 + s), (n1 / ns1) & 1, err, 14);
                 tc_fence_after();
                 if (lane == 0) {
                     const unsigned xa = smem_u32(stage1 + s * kStage1), aa = xa + kXTile;
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
                         tc_mma_f16(tmem + kD1Col + b1 * 64, make_desc(xa + k * 32, 2, 1024), make_desc(aa + k * 32, 2, 1024),
-                                   idesc1, (kb | k) != 0);
+                                   idesc1, ((kb - kb0) | k) != 0);
                     tc_commit(bar(EMPTY1 + s));                       // slot reusable once these MMAs finish
-                    if (kb == nkb - 1) tc_commit(bar(D1_FULL + b1));
+                    if (kb == kb1 - 1) tc_commit(bar(D1_FULL + b1));
                 }
                 __syncwarp();
             }
@@ -410,7 +437,10 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes: first warp of the quadrant
             if (half == 0) {
             float d1[64];
-            float* vrow = ws.v + ((size_t)proj * p.cap + t.pos0 + row) * kMaxRank;
+            // fp32 row of the intermediate: the reduced v, or this k part's slot when phase 1 is cut along k
+            const size_t vidx = ((size_t)proj * p.cap + t.pos0 + row) * kMaxRank;
+            const size_t kstride = (size_t)p.n_proj * p.cap * kMaxRank;
+            float* vrow = k_items ? ws.partial + part * kstride + vidx : ws.v + vidx;
             if (do1) {
                 const int b1 = n_item & 1;
                 mbar_wait(bar(D1_FULL + b1), (n_item >> 1) & 1, err, 18);
@@ -433,9 +463,43 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                             if (c * 4 < t.rank)
                                 reinterpret_cast<float4*>(vrow)[c] = make_float4(d1[4 * c], d1[4 * c + 1], d1[4 * c + 2], d1[4 * c + 3]);
                     }
+                    if (k_items) {
+                        // The CTA that finishes a pair's last k part adds the parts, in part order
+                        // whoever it is, into v.  Nobody waits: arrivals are counted per pair.
+                        __threadfence();
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (tid == 128) {
+                            const unsigned seen = atomicAdd(&ws.counters[rest], 1u);
+                            const bool last = seen == (unsigned)(ksplit - 1);
+                            if (last) ws.counters[rest] = 0u;             // zero at rest
+                            *last_flag = last ? 1 : 0;
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (*reinterpret_cast<volatile int*>(last_flag) != 0) {
+                            __threadfence();
+                            if (row < t.valid) {
+#pragma unroll
+                                for (int i = 0; i < 64; ++i) d1[i] = 0.f;
+                                for (int kp = 0; kp < ksplit; ++kp) {
+                                    const float4* src = reinterpret_cast<const float4*>(ws.partial + kp * kstride + vidx);
+#pragma unroll
+                                    for (int c = 0; c < 16; ++c)
+                                        if (c * 4 < t.rank) {
+                                            const float4 g = __ldcg(src + c);
+                                            d1[4 * c] += g.x; d1[4 * c + 1] += g.y; d1[4 * c + 2] += g.z; d1[4 * c + 3] += g.w;
+                                        }
+                                }
+#pragma unroll
+                                for (int c = 0; c < 16; ++c)
+                                    if (c * 4 < t.rank)
+                                        reinterpret_cast<float4*>(ws.v + vidx)[c] = make_float4(d1[4 * c], d1[4 * c + 1], d1[4 * c + 2], d1[4 * c + 3]);
+                            }
+                        }
+                    }
                     continue;
                 }
             } else {                                         // expand half only: v was summed by the caller
+                if (p.flags & kFlagLateWait) pdl_wait_prior();
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -475,12 +539,12 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const int nt0 = part * nnt_all / parts, nnt = (part + 1) * nnt_all / parts;
             const bool live = row < t.valid, whole = t.valid == kBM;
             for (int nt = nt0; nt < nnt; ++nt, ++nd) {
-                const int buf = nd & 1, ys = nd % kYS;
+                const int buf = nd & 1, ys = nd & (nys - 1);
                 // this thread's 128 bytes of the staged y block: row `row` of the box of its column half;
                 // the 16-byte chunk c of a row sits at chunk c ^ (row & 7)
                 unsigned char* ysm = ystage + ys * kYTile + half * (kYTile / 2) + row * 128;
                 uint4* yrow = reinterpret_cast<uint4*>(reinterpret_cast<T*>(pj.y) + (long long)(t.row0 + row) * pj.ldy + nt * kBN) + half * (kBN / 16);
-                if (y_staged) mbar_wait(bar(Y_FULL + ys), (nd / kYS) & 1, err, 22);
+                if (y_staged) mbar_wait(bar(Y_FULL + ys), (nd >> nys_log) & 1, err, 22);
                 mbar_wait(bar(D2_FULL + buf), (nd >> 1) & 1, err, 20);
                 tc_fence_after();
 #pragma unroll
@@ -549,9 +613,27 @@ cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    if (io_dtype == B200_LORA_F16) sgmv_tile_kernel<__half><<<n_sm, kSgmvThreads, kSgmvSmem, s>>>(p, sp);
-    else sgmv_tile_kernel<__nv_bfloat16><<<n_sm, kSgmvThreads, kSgmvSmem, s>>>(p, sp);
-    return cudaGetLastError();
+    auto launch = [&](const ApplyParams& q) {
+        if (io_dtype == B200_LORA_F16) sgmv_tile_kernel<__half><<<n_sm, kSgmvThreads, kSgmvSmem, s>>>(q, sp);
+        else sgmv_tile_kernel<__nv_bfloat16><<<n_sm, kSgmvThreads, kSgmvSmem, s>>>(q, sp);
+        return cudaGetLastError();
+    };
+    // With fewer (tile, projection) pairs than SMs a single launch has to cut every pair by output
+    // columns, and each part streams the pair's x rows again for phase 1 at the rate one SM's
+    // copy engine sustains.  Two launches avoid that: the first does phase 1 once per pair, cut
+    // along k over the idle SMs, and leaves fp32 sums in the workspace; the second cuts only
+    // phase 2.  The tile count is known on the device only; the token count bounds it.
+    const bool halves_given = (p.flags & (B200_LORA_ONLY_SHRINK | B200_LORA_ONLY_EXPAND)) != 0;
+    const long long max_pairs = ((long long)p.n_tokens / kBM + 1) * p.n_proj;
+    if (halves_given || max_pairs >= n_sm) return launch(p);
+    ApplyParams q = p;
+    q.flags = p.flags | B200_LORA_ONLY_SHRINK | kFlagKSplit;
+    cudaError_t e = launch(q);
+    if (e != cudaSuccess) return e;
+    q.flags = p.flags | B200_LORA_ONLY_EXPAND | kFlagLateWait;
+    if (io_dtype == B200_LORA_F16)
+        return launch_pdl(sgmv_tile_kernel<__half>, dim3(n_sm), dim3(kSgmvThreads), kSgmvSmem, s, q, sp);
+    return launch_pdl(sgmv_tile_kernel<__nv_bfloat16>, dim3(n_sm), dim3(kSgmvThreads), kSgmvSmem, s, q, sp);
 }
 
 }  // namespace b200lora
