@@ -261,8 +261,15 @@ def main():
             batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l, flags)
             batch.apply([(x_o[l], ys["o"][l], pools["o"])], l, flags)
 
-    # per layer two applies (q/k/v, o), each a shrink and an expand launch (plus the tile launch)
-    launches_per_pass = 1 + n_layers * (6 if use_tiles else 4)
+    # per layer two applies (q/k/v, o), each a shrink and an expand launch, plus with tiles the tile
+    # kernel: one launch, or two when the batch can hold fewer (tile, projection) pairs than the GPU
+    # has SMs (the library's own rule)
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+
+    def tile_launches(n_proj):
+        return 0 if not use_tiles else (2 if (T // 128 + 1) * n_proj < n_sm else 1)
+
+    launches_per_pass = 1 + n_layers * (4 + tile_launches(3) + tile_launches(1))
 
     def capture(flags=0, plan=True):
         g = torch.cuda.CUDAGraph()
