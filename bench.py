@@ -201,7 +201,9 @@ def tensor_parallel_arm(args, wl, rank, local, world, dev):
                          "achieved": per_gpu / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": per_gpu / (ms * 1e-3) / 1e9 / peak, "traffic": None},
             "cpu_baseline": None, "e2e": None,
-            "gpu_launches": (1 + n_layers * 4) * args.steps, "clocks": clk.summary(),
+            # per layer two applies, each shrink + fold + expand, and with tiles one tile launch per half
+            "gpu_launches": (1 + n_layers * 2 * (3 + (2 if wl.seq_lens is not None else 0))) * args.steps,
+            "clocks": clk.summary(),
         }
         print(json.dumps(out), flush=True)
 
