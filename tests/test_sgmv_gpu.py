@@ -132,3 +132,37 @@ def test_full_size_prefill_batch():
     # the reference's rounding of the intermediate (its prefill op keeps fp16 tensors)
     y_mid = run_segments(c, 0, y_dtype=torch.float32, flags=L.MID_ROUND)
     assert rel_err(y_mid.double().cpu().numpy(), c.oracle_delta(0, mid_round="fp16")) <= TOL
+
+
+def test_few_whole_tiles_three_projections_cut_along_k():
+    """Few tiles (two launches: phase 1 cut eight ways along k, then phase 2 by columns), three projections
+    of different widths in one call, runs of whole 128-row tiles (their y leaves by tensor store) next to a
+    partial one, and an output width that ends in half a 128-column slice."""
+    lens, adapters, ranks = [256, 128, 100, 384], [3, 0, 2, 1], [64, 16, 32, 32]
+    cases = [seg_case(lens, adapters, ranks, 4, 1024, h_out, "bf16", seed=40 + i) for i, h_out in enumerate((320, 128, 576))]
+    T = cases[0].T
+    batch = L.LoraBatch(T, 4, 1024, 3)
+    batch.set_segments(cases[0].seg_starts, cases[0].seg_adapter, T, cases[0].pool, tiles=True)
+
+    def run(y_dtype):
+        ys = [torch.zeros(T, c.h_out, dtype=y_dtype, device="cuda") for c in cases]
+        batch.apply([(c.x, y, c.pool) for c, y in zip(cases, ys)], 1)
+        torch.cuda.synchronize()
+        batch.workspace.check()
+        return ys
+
+    y32, y16 = run(torch.float32), run(torch.bfloat16)
+    for c, a, b in zip(cases, y32, y16):
+        assert rel_err(a.double().cpu().numpy(), c.oracle_delta(1)) <= TOL
+        assert torch.equal(b, a.to(torch.bfloat16))            # one rounding of the fp32 result
+    for a, b in zip(run(torch.bfloat16), y16):
+        assert torch.equal(a, b)                               # reproducible whichever CTA adds the k parts
+    # y that is not zero: the update adds to what is there
+    base = [torch.randn(T, c.h_out, device="cuda").to(torch.bfloat16) for c in cases]
+    ys = [b.clone() for b in base]
+    batch.apply([(c.x, y, c.pool) for c, y in zip(cases, ys)], 1)
+    torch.cuda.synchronize()
+    for b, y, d in zip(base, ys, y32):
+        want = b.float() + d
+        # bf16 output of a fused multiply-add: within one bf16 step of the separately rounded sum
+        assert float((y.float() - want).abs().max()) <= float(want.abs().max()) * 2.0 ** -7
