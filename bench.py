@@ -364,9 +364,18 @@ def main():
     # end to end from pinned host buffers through the public ops
     e2e = None
     if not args.no_e2e:
-        hx_qkv = torch.empty(x_qkv.shape, dtype=dt).pin_memory().copy_(x_qkv.cpu())
-        hx_o = torch.empty(x_o.shape, dtype=dt).pin_memory().copy_(x_o.cpu())
-        hy = {n: torch.empty(ys[n].shape, dtype=dt).pin_memory() for n in names}
+        # One host->device copy and one device->host copy per layer: the layer's two activations sit
+        # side by side in one buffer, and so do its four outputs (each projection's y is a column
+        # range of the layer's [T, sum(h_out)] block; the kernels take the row pitch).
+        h_in0 = wl.projections[0].h_in
+        widths = [p.h_out for p in wl.projections]
+        offs = [sum(widths[:i]) for i in range(len(widths))]
+        dx = torch.empty(n_layers, 2, T, h_in0, dtype=dt, device=dev)
+        dx[:, 0].copy_(x_qkv); dx[:, 1].copy_(x_o)
+        hx = torch.empty(dx.shape, dtype=dt).pin_memory().copy_(dx.cpu())
+        y_all = torch.zeros(n_layers, T, sum(widths), dtype=dt, device=dev)
+        yv = {n: y_all[:, :, o:o + w] for n, o, w in zip(names, offs, widths)}
+        hy = torch.empty(y_all.shape, dtype=dt).pin_memory()
         copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
         def e2e_step():
@@ -376,20 +385,18 @@ def main():
             ev_in, ev_done = [], []
             with torch.cuda.stream(copy_in):
                 for l in range(n_layers):
-                    x_qkv[l].copy_(hx_qkv[l], non_blocking=True)
-                    x_o[l].copy_(hx_o[l], non_blocking=True)
+                    dx[l].copy_(hx[l], non_blocking=True)
                     ev = torch.cuda.Event(); ev.record(copy_in); ev_in.append(ev)
             with torch.cuda.stream(stream):
                 for l in range(n_layers):
                     stream.wait_event(ev_in[l])
-                    batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
-                    batch.apply([(x_o[l], ys["o"][l], pools["o"])], l)
+                    batch.apply([(dx[l, 0], yv[n][l], pools[n]) for n in names if n != "o"], l)
+                    batch.apply([(dx[l, 1], yv["o"][l], pools["o"])], l)
                     ev = torch.cuda.Event(); ev.record(stream); ev_done.append(ev)
             with torch.cuda.stream(copy_out):
                 for l in range(n_layers):
                     copy_out.wait_event(ev_done[l])
-                    for n in names:
-                        hy[n][l].copy_(ys[n][l], non_blocking=True)
+                    hy[l].copy_(y_all[l], non_blocking=True)
             stream.wait_stream(copy_out)
 
         for _ in range(2):
@@ -411,8 +418,8 @@ def main():
             tms = torch.tensor([ms_e2e], device=dev)
             dist.all_reduce(tms, op=dist.ReduceOp.MAX)
             ms_e2e = float(tms.item())
-        h2d = (hx_qkv.numel() + hx_o.numel()) * 2 + ids_host.numel() * 4
-        d2h = sum(hy[n].numel() for n in names) * 2
+        h2d = hx.numel() * 2 + ids_host.numel() * 4
+        d2h = hy.numel() * 2
         e2e = {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e}
 

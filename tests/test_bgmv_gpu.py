@@ -109,6 +109,33 @@ def test_fused_qkv_equals_separate_calls():
     assert close(ys[1], k.run(1))
 
 
+def test_outputs_side_by_side_in_one_buffer():
+    """q | k | v as column ranges of one [T, sum(h_out)] block (row pitch larger than the width), x as
+    one of two activations that share a buffer: same bits as separate contiguous tensors, nothing
+    written outside the ranges.  Decode kernels and, with tall runs, the tile kernel."""
+    for tiles, ids in ((False, None), (True, np.concatenate([np.arange(40) % 6, np.repeat([7, 2], [128, 70])]).astype(np.int32))):
+        T = 48 if ids is None else len(ids)
+        c = Case(T, 12, 1024, 1024, [16, 64], "bf16", seed=31, zipf=1.0 if ids is None else None, ids=ids)
+        k = Case(T, 12, 1024, 256, c.ranks, "bf16", seed=32, ids=c.ids)
+        pools, widths = [c.pool, k.pool, c.pool], [1024, 256, 1024]
+        xx = torch.zeros(2, T, 1024, dtype=torch.bfloat16, device="cuda")
+        xx[1].copy_(c.x)
+        g = torch.Generator().manual_seed(9)
+        block = torch.randn(T, sum(widths) + 64, generator=g).to(torch.bfloat16).cuda()     # 64 canary columns
+        sep = [block[:, o:o + w].clone() for o, w in zip((0, 1024, 1280), widths)]
+        before = block.clone()
+        views = [block[:, o:o + w] for o, w in zip((0, 1024, 1280), widths)]
+        batch = L.LoraBatch(T, 12, 1024, 3).set_ids(c.ids_dev, c.pool, tiles=tiles)
+        batch.apply([(xx[1], v, p) for v, p in zip(views, pools)], 1)
+        batch.apply([(c.x, y, p) for y, p in zip(sep, pools)], 1)
+        torch.cuda.synchronize()
+        batch.workspace.check()
+        for v, y in zip(views, sep):
+            assert torch.equal(v, y)
+        assert torch.equal(block[:, sum(widths):], before[:, sum(widths):])
+        assert not torch.equal(views[0], before[:, :1024])
+
+
 def test_errors_are_raised_not_swallowed():
     c = Case(8, 4, 128, 128, 8, "fp16", seed=1)
     bad = c.ids_dev.clone()
