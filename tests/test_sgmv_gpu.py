@@ -119,8 +119,8 @@ def test_mixed_decode_and_prefill_from_ids():
 
 
 def test_full_size_prefill_batch():
-    """The prefill workload at full size (16 prompts of 128..1024 tokens, rank 32, hidden 4096): more
-    (tile, projection) pairs than CTAs, so the last round of pairs is cut by output columns."""
+    """The prefill workload at full size (16 prompts of 128..1024 tokens, rank 32, hidden 4096), one
+    projection: 73 tiles, so phase 1 is cut in two along k and phase 2 by output columns."""
     lens = [537, 824, 517, 341, 399, 247, 211, 845, 932, 822, 305, 334, 379, 996, 658, 989]
     c = seg_case(lens, list(range(16)), [32] * 16, 16, 4096, 4096, "fp16", seed=2962)
     want = c.oracle_delta(0)
@@ -166,3 +166,31 @@ def test_few_whole_tiles_three_projections_cut_along_k():
         want = b.float() + d
         # bf16 output of a fused multiply-add: within one bf16 step of the separately rounded sum
         assert float((y.float() - want).abs().max()) <= float(want.abs().max()) * 2.0 ** -7
+
+
+def test_more_pairs_than_sms_single_launch():
+    """Enough tiles that both phases run in one launch per apply (at least as many (tile, projection)
+    pairs as SMs): full rounds of whole pairs, then a last round cut by output columns."""
+    rng = np.random.default_rng(77)
+    lens = [int(v) for v in rng.integers(300, 700, 14)]          # about 7000 rows: over 50 tiles, three projections
+    ranks = [int(v) for v in rng.choice([16, 32, 64], 14)]
+    cases = [seg_case(lens, list(range(14)), ranks, 14, 1024, h_out, "fp16", seed=60 + i) for i, h_out in enumerate((1024, 256, 1024))]
+    T = cases[0].T
+    n_sm = torch.cuda.get_device_properties(0).multi_processor_count
+    assert (T // 128 + 1) * 3 >= n_sm
+    batch = L.LoraBatch(T, 14, 1024, 3)
+    batch.set_segments(cases[0].seg_starts, cases[0].seg_adapter, T, cases[0].pool, tiles=True)
+
+    def run(y_dtype):
+        ys = [torch.zeros(T, c.h_out, dtype=y_dtype, device="cuda") for c in cases]
+        batch.apply([(c.x, y, c.pool) for c, y in zip(cases, ys)], 0)
+        torch.cuda.synchronize()
+        batch.workspace.check()
+        return ys
+
+    y32, y16 = run(torch.float32), run(torch.float16)
+    for c, a, b in zip(cases, y32, y16):
+        assert rel_err(a.double().cpu().numpy(), c.oracle_delta(0)) <= TOL
+        assert torch.equal(b, a.to(torch.float16))
+    for a, b in zip(run(torch.float16), y16):
+        assert torch.equal(a, b)
