@@ -48,8 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         print(res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building libb200lora.so")
-    with open(os.path.join(LIB_DIR, "ptxas.log"), "w") as f:
-        f.write(res.stderr)
+    with open(os.path.join(LIB_DIR, "ptxas.log"), "w") as f:      # registers, spills, shared memory per kernel
+        f.write("".join(l for l in res.stderr.splitlines(True) if "Compile time" not in l))
     return LIB_PATH
 
 
