@@ -627,10 +627,7 @@ cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io
     const long long max_pairs = ((long long)p.n_tokens / kBM + 1) * p.n_proj;
     if (max_pairs >= n_sm) return launch(p);
     ApplyParams q = p;
-    if (halves_given) {                  // the caller's shrink half spreads along k in the same way
-        if (p.flags & B200_LORA_ONLY_SHRINK) q.flags |= kFlagKSplit;
-        return launch(q);
-    }
+    if (halves_given) return launch(q);
     q.flags = p.flags | B200_LORA_ONLY_SHRINK | kFlagKSplit;
     cudaError_t e = launch(q);
     if (e != cudaSuccess) return e;
