@@ -7,7 +7,8 @@ interface of the reference's LoRA layer objects.
 from . import workloads                                      # noqa: F401
 from .pool import AdapterPool, MAX_RANK                      # noqa: F401
 from ._lib import LoraError, MID_ROUND, NO_TENSOR, DELTA_THEN_ADD   # noqa: F401
-from .ops import (LoraBatch, LoraPlan, LoraWorkspace, add_lora_bgmv, add_lora_bgmv_static,   # noqa: F401
-                  add_lora_bgmv_v2, add_lora_sgmv, adapters_of, apply)
+from .ops import (LoraBatch, LoraPlan, LoraWorkspace, add_lora_bgmv, add_lora_bgmv_once,   # noqa: F401
+                  add_lora_bgmv_static, add_lora_bgmv_static_status, add_lora_bgmv_v2, add_lora_sgmv,
+                  add_lora_bgmv_workspace_bytes, adapters_of, apply, invalidate_plan_cache)
 from . import ops                                            # noqa: F401
 from .lora_gpu import Lora_GPU                               # noqa: F401

@@ -67,6 +67,7 @@ SYMBOLS = {
     "b200_add_lora_bgmv_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                             C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_int32, C.c_float, C.c_int32, C.c_void_p]),
+    "b200_add_lora_bgmv_static_status": (C.c_int, [C.c_void_p]),
 }
 
 _LIB = None

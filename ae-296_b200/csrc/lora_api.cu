@@ -110,6 +110,12 @@ bool fast_ranks(const b200_lora_adapters* ad) {
     return ad->ranks_pow2 != 0 && (ad->packed || pow2);
 }
 
+// the workspace's sticky error word as a status code
+int status_of_error_word(unsigned word) {
+    if (word == 0u) return B200_LORA_OK;
+    return word >= kErrPlanMismatch ? B200_LORA_ERR_DIM : B200_LORA_ERR_TIMEOUT;
+}
+
 PlanAdapters plan_adapters(const b200_lora_adapters* ad) {
     PlanAdapters pa;
     pa.ranks = ad->ranks;
@@ -127,6 +133,30 @@ PlanAdapters plan_adapters(const b200_lora_adapters* ad) {
 // Scratch for b200_add_lora_bgmv_static: plan + workspace of the largest accepted call.  It
 // lives in the library image, so every GPU that loads the library carries it until exit.
 static __device__ __align__(256) unsigned char g_static_scratch[B200_LORA_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};      // device address of the array, per device (guarded by the mutex)
+size_t g_static_last_pb[64] = {0};       // plan bytes of the last static call, per device
+
+// One-time set-up per device: in host code `g_static_scratch` is only a stand-in for the device
+// array, so its device address has to be asked for, with that device current.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (dev < 0 || dev >= 64) return B200_LORA_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e);
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return B200_LORA_OK;
+}
+}  // namespace
 
 extern "C" {
 
@@ -314,7 +344,7 @@ int b200_lora_workspace_status(const void* workspace, void* stream) {
     cudaError_t e = cudaMemcpyAsync(&ctl, workspace, sizeof(ctl), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return cuda_fail(e);
-    return ctl.error ? B200_LORA_ERR_TIMEOUT : B200_LORA_OK;
+    return status_of_error_word(ctl.error);
 }
 
 size_t b200_add_lora_bgmv_workspace_bytes(int32_t n_tokens, int32_t n_adapters, int32_t h_in) {
@@ -337,6 +367,11 @@ int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void*
     ad.n_adapters = n_adapters; ad.n_layers = n_layers; ad.r_pool = r; ad.packed = 0; ad.scale = scale;
     size_t pb = (b200_lora_plan_bytes(n_tokens, n_adapters) + 255) & ~size_t(255);
     char* ws = static_cast<char*>(workspace) + pb;
+    // Where the control words sit depends on this call's n_tokens and n_adapters, so a buffer that
+    // served a call of another shape holds that call's records or partial sums there: clear them
+    // (error word and arrival counters must start at zero) on every call.
+    cudaError_t ce = cudaMemsetAsync(ws, 0, ws_ctl_bytes(n_tokens), static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return cuda_fail(ce);
     int rc = b200_lora_plan_build(workspace, pb, n_tokens, indicies, indicies_are_i64, n_tokens, &ad, stream);
     if (rc) return rc;
     b200_lora_proj pj;
@@ -357,29 +392,46 @@ int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, cons
     const size_t need = b200_add_lora_bgmv_workspace_bytes(n_tokens, n_adapters, h_in);
     if (need == 0 || need > (size_t)B200_LORA_STATIC_SCRATCH_BYTES) return B200_LORA_ERR_WORKSPACE;
 
-    // One-time set-up per device: in host code `g_static_scratch` is only a stand-in for the
-    // device array, so its device address has to be asked for, with that device current.
-    static void* dev_ptr[64] = {nullptr};
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return cuda_fail(e);
-    if (dev < 0 || dev >= 64) return B200_LORA_ERR_UNSUPPORTED;
-    if (!dev_ptr[dev]) {
-        void* ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-        if (e != cudaSuccess) return cuda_fail(e);
-        dev_ptr[dev] = ptr;
-    }
-    void* scratch = dev_ptr[dev];
-    // The array keeps whatever the previous call left.  The kernels need their control words
-    // (arrival counters, error word) to start at zero: clear that prefix of the workspace part;
-    // the plan part is rebuilt from scratch by every call.
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);       // the first call on a device looks the address up
+    if (rc) return rc;
+    // The array keeps whatever the previous call left; b200_add_lora_bgmv clears the control
+    // words (arrival counters, error word) of this call's layout and rebuilds the plan.
     const size_t pb = (b200_lora_plan_bytes(n_tokens, n_adapters) + 255) & ~size_t(255);
-    e = cudaMemsetAsync(static_cast<char*>(scratch) + pb, 0, ws_ctl_bytes(n_tokens), static_cast<cudaStream_t>(stream));
-    if (e != cudaSuccess) return cuda_fail(e);
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        g_static_last_pb[dev] = pb;              // where the last call's workspace part begins
+    }
     return b200_add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, indicies_are_i64, n_tokens, h_in, h_out,
                               n_adapters, n_layers, r, layer_idx, scale, dtype, scratch,
                               (size_t)B200_LORA_STATIC_SCRATCH_BYTES, stream);
+}
+
+int b200_add_lora_bgmv_static_status(void* stream) {
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    size_t pb;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        pb = g_static_last_pb[dev];
+    }
+    if (pb == 0) return B200_LORA_OK;            // no call yet on this device
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PlanHeader h;
+    WorkspaceCtl ctl;
+    cudaError_t e = cudaMemcpyAsync(&h, scratch, sizeof(h), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&ctl, static_cast<char*>(scratch) + pb, sizeof(ctl), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (h.error == 1) return B200_LORA_ERR_ID_RANGE;
+    if (h.error == 3) return B200_LORA_ERR_RANK;
+    if (h.error) return B200_LORA_ERR_SEGMENTS;
+    return status_of_error_word(ctl.error);
 }
 
 }  // extern "C"

@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) bgmv_shrink_kernel(const __gri
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
+    if (!plan_usable(hdr, p, &ws.ctl->error)) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_in;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -520,7 +520,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) bgmv_expand_kernel(const __gri
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
+    if (!plan_usable(hdr, p, &ws.ctl->error)) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_out;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
+    if (!plan_usable(hdr, p, &ws.ctl->error)) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_in;
     // each CTA takes a contiguous range of items
@@ -824,7 +824,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
+    if (!plan_usable(hdr, p, &ws.ctl->error)) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int n_items = n_units * p.total_super_out;
     const int per_cta = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -934,7 +934,7 @@ __global__ void __launch_bounds__(128) fold_partials_kernel(const __grid_constan
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
-    if (hdr.error || hdr.cap != p.cap) return;
+    if (!plan_usable(hdr, p, &ws.ctl->error)) return;
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int per_cta = (n_units * p.total_super_in + shrink_grid - 1) / shrink_grid;
     const int proj = blockIdx.y;

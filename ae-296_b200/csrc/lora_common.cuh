@@ -191,6 +191,22 @@ __device__ __forceinline__ long long block_row0(const ApplyParams& p, const Unit
 }
 __device__ __forceinline__ int b_pitch(const ApplyParams& p, int r) { return p.packed ? r : p.r_pool; }
 
+// Values of the workspace's sticky error word: 1..15 name the bounded wait that expired, this one
+// says that an apply call was given a plan built for another capacity or another number of rows.
+constexpr unsigned kErrPlanMismatch = 64u;
+
+// May this apply walk the plan?  A plan whose build failed applies nothing (its own error word
+// tells why); a plan built for other sizes would index x and y out of range, so it applies
+// nothing either and the workspace's error word records it.
+__device__ __forceinline__ bool plan_usable(const PlanHeader& hdr, const ApplyParams& p, unsigned* err) {
+    if (hdr.error) return false;
+    if (hdr.cap != p.cap || hdr.n_tokens != p.n_tokens) {
+        if (threadIdx.x == 0) atomicMax(err, kErrPlanMismatch);
+        return false;
+    }
+    return true;
+}
+
 __host__ __device__ __forceinline__ int pad_rank(int r) { return r <= 8 ? 8 : r <= 16 ? 16 : r <= 32 ? 32 : 64; }
 // sub-ranges per 2048-wide super-chunk for a padded rank: 8->4, 16->4, 32->8, 64->16, i.e. a unit is
 // 512 / 512 / 256 / 128 columns (shrink) or rows (expand) wide and holds <= 16 KB of weights

@@ -215,7 +215,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const PlanHeader hdr = *pv.hdr;
     unsigned* err = &ws.ctl->error;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n_tiles = (hdr.error || hdr.cap != p.cap) ? 0 : hdr.n_tiles;
+    const int n_tiles = plan_usable(hdr, p, err) ? hdr.n_tiles : 0;
     // Work items: (tile, projection) pairs, dealt to the CTAs round by round.  The pairs of the
     // last, incomplete round are cut by output columns into `nsplit` parts each (every part redoes
     // the cheap phase 1, mostly from L2), so that the round keeps all SMs busy for a fraction of a

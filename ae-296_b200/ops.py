@@ -11,6 +11,7 @@ library, and there is no fallback path.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -66,11 +67,13 @@ class LoraPlan:
         self.buf = torch.zeros((nbytes + 15) // 16 * 2, dtype=torch.int64, device=device)
         self.nbytes = self.buf.numel() * 8
         self._keep = None
+        self.n_tokens = 0            # rows of the batch the plan was last built for
 
     def build(self, ids: torch.Tensor, adapters: Adapters) -> "LoraPlan":
         _require_cuda(ids)
         if ids.dtype not in (torch.int32, torch.int64) or not ids.is_contiguous():
             raise ValueError("ids must be a contiguous int32/int64 tensor")
+        self.n_tokens = int(ids.numel())
         check(_lib.lib().b200_lora_plan_build(
             self.buf.data_ptr(), self.nbytes, self.max_tokens, ids.data_ptr(),
             1 if ids.dtype == torch.int64 else 0, ids.numel(), C.byref(adapters), _stream(ids.device)),
@@ -83,6 +86,7 @@ class LoraPlan:
         if seg_starts.dtype != torch.int32 or seg_adapter.dtype != torch.int32:
             raise ValueError("segment tables must be int32")
         self._keep = (seg_starts, seg_adapter)
+        self.n_tokens = int(n_tokens)
         check(_lib.lib().b200_lora_plan_from_segments(
             self.buf.data_ptr(), self.nbytes, self.max_tokens, seg_starts.data_ptr(), seg_adapter.data_ptr(),
             seg_adapter.numel(), int(n_tokens), C.byref(adapters), _stream(seg_starts.device)),
@@ -154,8 +158,8 @@ def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan:
             io, ydt = x.dtype, y.dtype
         if x.dtype != io or y.dtype != ydt or ydt not in (io, torch.float32):
             raise ValueError("all projections share the I/O dtype; y is that dtype or fp32")
-        if x.shape[0] > plan.max_tokens:
-            raise ValueError("more tokens than the plan was sized for")
+        if x.shape[0] != plan.n_tokens:
+            raise ValueError(f"the plan was built for {plan.n_tokens} rows, x has {x.shape[0]}")
         arr[i] = Proj(x.data_ptr(), y.data_ptr(), pool.wa.data_ptr(), pool.wb.data_ptr(),
                       x.stride(0), y.stride(0), pool.h_in, pool.h_out)
     ad = adapters if adapters is not None else adapters_of(projs[0][2])
@@ -165,17 +169,54 @@ def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan:
         int(flags), workspace.buf.data_ptr(), workspace.nbytes, _stream(projs[0][0].device)), "apply")
 
 
-# ---- cached scratch for the one-call ops -------------------------------------------------------
-_SCRATCH = {}
+# ---- the reference's operator call ---------------------------------------------------------------
+class _OpState:
+    """Plan + workspace behind :func:`add_lora_bgmv` for one (device, stream), and what the plan
+    was built from."""
+
+    def __init__(self):
+        self.batch: Optional[LoraBatch] = None
+        self.dims = (0, 0, 0)            # capacity: tokens, adapters, h_in
+        self.key = None
+        self.ids_ref = None
 
 
-def _scratch(device, nbytes: int) -> torch.Tensor:
-    key = (torch.device(device).index, _stream(device))
-    buf = _SCRATCH.get(key)
-    if buf is None or buf.numel() * 8 < nbytes:
-        buf = torch.zeros((nbytes + 15) // 16 * 2, dtype=torch.int64, device=device)
-        _SCRATCH[key] = buf
-    return buf
+_OP_STATE = {}
+
+
+def invalidate_plan_cache() -> None:
+    """Forget the plans :func:`add_lora_bgmv` keeps.  Needed only after the contents of an index
+    tensor were changed behind torch's back (a custom kernel or a raw pointer write, which do not
+    bump the tensor's version counter)."""
+    for st in _OP_STATE.values():
+        st.key, st.ids_ref = None, None
+
+
+def _plan_for(ids: torch.Tensor, t: int, n: int, r: int, h_in: int, scale: float, ad: Adapters) -> LoraBatch:
+    """The plan of ``ids``, rebuilt only when it can have changed.
+
+    The reference's decode loop calls the op 3 x n_layers times per step with the SAME index tensor
+    (lightllm/models/lora_gpu.py:138,150,162 with ``select_inds[bsz-1]``).  The plan depends on
+    the ids, N, r and the scale only, so it is kept while the very same tensor object is passed
+    again unmodified (torch's version counter) and rebuilt otherwise.  During CUDA-graph capture
+    it is always rebuilt inside the graph, because a replay does not come back here."""
+    dev = ids.device
+    skey = (dev.index, _stream(dev))
+    st = _OP_STATE.get(skey)
+    if st is None:
+        st = _OP_STATE[skey] = _OpState()
+    if st.batch is None or t > st.dims[0] or n > st.dims[1] or h_in > st.dims[2]:
+        st.dims = (max(t, st.dims[0]), max(n, st.dims[1]), max(h_in, st.dims[2]))
+        st.batch = LoraBatch(st.dims[0], st.dims[1], st.dims[2], 1, dev)
+        st.key = None
+    key = (ids.data_ptr(), ids._version, ids.dtype, t, n, r, float(scale))
+    capturing = torch.cuda.is_current_stream_capturing()
+    same = (not capturing and st.key == key and st.ids_ref is not None and st.ids_ref() is ids)
+    if not same:
+        st.batch.plan.build(ids, ad)
+        st.key = None if capturing else key
+        st.ids_ref = None if capturing else weakref.ref(ids)
+    return st.batch
 
 
 def add_lora_bgmv(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T_all: torch.Tensor,
@@ -185,6 +226,9 @@ def add_lora_bgmv(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T
     Same arguments as the reference's decode op: ``y [T, h_out]``, ``x [T, h_in]``,
     ``wa_T_all [N, L, r, h_in]``, ``wb_T_all [N, L, h_out, r]`` contiguous fp16/bf16 CUDA
     tensors, ``indicies [T]`` int64 (or int32) CUDA tensor.  Returns ``None``.
+
+    Two launches (shrink, expand) when the index tensor is the one of the previous call on this
+    stream, unmodified; one more (the plan kernel) when it is new.
     """
     _require_cuda(y, x, wa_T_all, wb_T_all, indicies)
     if wa_T_all.dim() != 4 or wb_T_all.dim() != 4:
@@ -203,15 +247,34 @@ def add_lora_bgmv(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T
         raise ValueError("fp16 or bf16 tensors of one dtype expected")
     if indicies.dtype not in (torch.int32, torch.int64):
         raise ValueError("indicies must be int32 or int64")
-    L = _lib.lib()
-    nbytes = L.b200_add_lora_bgmv_workspace_bytes(t, n, h_in)
-    if nbytes == 0:
-        raise ValueError("bad dimensions")
-    ws = _scratch(x.device, nbytes)
-    check(L.b200_add_lora_bgmv(
+    ad = _adapters_struct(n, l, r, scale=scale)
+    batch = _plan_for(indicies, t, n, r, h_in, scale, ad)
+    arr = (Proj * 1)(Proj(x.data_ptr(), y.data_ptr(), wa_T_all.data_ptr(), wb_T_all.data_ptr(), h_in, h_out, h_in, h_out))
+    check(_lib.lib().b200_lora_apply(
+        arr, 1, C.byref(ad), batch.plan.buf.data_ptr(), batch.plan.max_tokens, t, int(layer_idx), _DT[x.dtype],
+        _DT[x.dtype], _lib.NO_TENSOR, batch.workspace.buf.data_ptr(), batch.workspace.nbytes, _stream(x.device)),
+        "add_lora_bgmv")
+
+
+def add_lora_bgmv_once(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T_all: torch.Tensor,
+                       indicies: torch.Tensor, layer_idx: int, scale: float, workspace: torch.Tensor) -> None:
+    """The same op as ONE C-ABI call (``b200_add_lora_bgmv``): plan and scratch live in the
+    caller's ``workspace`` (any dtype, ``b200_add_lora_bgmv_workspace_bytes`` bytes or more, no
+    preparation needed) and the plan is rebuilt by every call.  For bindings that cannot keep
+    state between calls; tensors as for :func:`add_lora_bgmv`, shapes are not re-validated."""
+    _require_cuda(y, x, wa_T_all, wb_T_all, indicies, workspace)
+    n, l, r, h_in = wa_T_all.shape
+    h_out = wb_T_all.shape[2]
+    t = x.shape[0]
+    check(_lib.lib().b200_add_lora_bgmv(
         y.data_ptr(), x.data_ptr(), wa_T_all.data_ptr(), wb_T_all.data_ptr(), indicies.data_ptr(),
         1 if indicies.dtype == torch.int64 else 0, t, h_in, h_out, n, l, r, int(layer_idx), float(scale),
-        _DT[x.dtype], ws.data_ptr(), ws.numel() * 8, _stream(x.device)), "add_lora_bgmv")
+        _DT[x.dtype], workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream(x.device)),
+        "add_lora_bgmv")
+
+
+def add_lora_bgmv_workspace_bytes(n_tokens: int, n_adapters: int, h_in: int) -> int:
+    return int(_lib.lib().b200_add_lora_bgmv_workspace_bytes(n_tokens, n_adapters, h_in))
 
 
 def add_lora_bgmv_static(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tensor, wb_T_all: torch.Tensor,
@@ -243,6 +306,14 @@ def add_lora_bgmv_static(y: torch.Tensor, x: torch.Tensor, wa_T_all: torch.Tenso
         y.data_ptr(), x.data_ptr(), wa_T_all.data_ptr(), wb_T_all.data_ptr(), indicies.data_ptr(),
         1 if indicies.dtype == torch.int64 else 0, t, h_in, h_out, n, l, r, int(layer_idx), float(scale),
         _DT[x.dtype], _stream(x.device)), "add_lora_bgmv_static")
+
+
+def add_lora_bgmv_static_status(device=None) -> None:
+    """Synchronises and raises if the last :func:`add_lora_bgmv_static` call on ``device`` saw an
+    adapter id out of range (that call left ``y`` unchanged) or an expired device-side wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        check(_lib.lib().b200_add_lora_bgmv_static_status(_stream(dev)), "add_lora_bgmv_static_status")
 
 
 class LoraBatch:

@@ -146,14 +146,17 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
 int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* offset_bytes, size_t* size_bytes);
 
 /* Reads the workspace's sticky device-side error word (synchronises `stream`):
- * B200_LORA_OK, or B200_LORA_ERR_TIMEOUT if a bounded wait inside a kernel expired. */
+ * B200_LORA_OK, B200_LORA_ERR_TIMEOUT if a bounded wait inside a kernel expired, or
+ * B200_LORA_ERR_DIM if an apply was given a plan built for another max_tokens or n_tokens
+ * (such an apply changes nothing: the plan's token rows would not fit x and y). */
 int b200_lora_workspace_status(const void* workspace, void* stream);
 
 /* ---- the reference's operator call -------------------------------------------------------
  * Same arguments as punica.ops.add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx,
  * scale) at lightllm/models/lora_gpu.py:138,150,162, flattened to pointers and sizes.
- * Builds a plan inside `workspace` and applies one projection.  `workspace` must have been
- * zero-filled once (b200_lora_workspace_init) after allocation. */
+ * Builds a plan inside `workspace` and applies one projection.  `workspace` needs no
+ * preparation and may be reused by calls of any shape that fit it: every call clears the
+ * control words of its own layout. */
 size_t b200_add_lora_bgmv_workspace_bytes(int32_t n_tokens, int32_t n_adapters, int32_t h_in);
 int b200_add_lora_bgmv(void* y, const void* x, const void* wa_T_all, const void* wb_T_all,
                        const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
@@ -188,6 +191,12 @@ int b200_add_lora_bgmv_static(void* y, const void* x, const void* wa_T_all, cons
                               const void* indicies, int32_t indicies_are_i64, int32_t n_tokens,
                               int32_t h_in, int32_t h_out, int32_t n_adapters, int32_t n_layers, int32_t r,
                               int32_t layer_idx, float scale, int32_t dtype, void* stream);
+/* Outcome of the last b200_add_lora_bgmv_static call on the current device, read back from the
+ * built-in array (synchronises `stream`; no counterpart in the reference): B200_LORA_OK, or
+ * what b200_lora_plan_read / b200_lora_workspace_status would report for that call
+ * (an adapter id outside [0, N) leaves y unchanged; an expired device wait).  The next
+ * static call overwrites it. */
+int b200_add_lora_bgmv_static_status(void* stream);
 
 #ifdef __cplusplus
 }

@@ -67,3 +67,31 @@ class Case:
 def rel_err(got64: np.ndarray, want64: np.ndarray) -> float:
     rms = float(np.sqrt((want64 ** 2).mean()))
     return float(np.abs(got64 - want64).max() / max(rms, 1e-30))
+
+
+def shared_x_cases(T, N, h_in, h_outs, ranks, dtype, ids, seed, n_layers=1, dense=False):
+    """One Case per output width, all with the same activation, ids and ranks (the q/k/v
+    projections of one layer share x)."""
+    first = Case(T, N, h_in, h_outs[0], ranks, dtype, dense=dense, seed=seed, n_layers=n_layers, ids=ids)
+    cases = [first] + [Case(T, N, h_in, h, first.ranks, dtype, dense=dense, seed=seed + i, n_layers=n_layers, ids=ids)
+                       for i, h in enumerate(h_outs[1:], 1)]     # one adapter table (ranks) for all of them
+    for c in cases[1:]:
+        c.x, c.x_cpu = cases[0].x, cases[0].x_cpu
+    return cases
+
+
+def raw_apply(projs, plan, layer, workspace, n_tokens, flags=0, adapters=None):
+    """``b200_lora_apply`` called directly with an explicit ``n_tokens`` (the Python wrapper
+    refuses a row count that differs from the plan's before the library sees it)."""
+    import ctypes as C
+    from ae296_b200 import _lib
+    from ae296_b200.ops import _DT, adapters_of
+    arr = (_lib.Proj * len(projs))()
+    for i, (x, y, pool) in enumerate(projs):
+        arr[i] = _lib.Proj(x.data_ptr(), y.data_ptr(), pool.wa.data_ptr(), pool.wb.data_ptr(),
+                           x.stride(0), y.stride(0), pool.h_in, pool.h_out)
+    ad = adapters if adapters is not None else adapters_of(projs[0][2])
+    x0, y0 = projs[0][0], projs[0][1]
+    return _lib.lib().b200_lora_apply(arr, len(projs), C.byref(ad), plan.buf.data_ptr(), plan.max_tokens, n_tokens,
+                                      layer, _DT[x0.dtype], _DT[y0.dtype], flags, workspace.buf.data_ptr(),
+                                      workspace.nbytes, torch.cuda.current_stream().cuda_stream)

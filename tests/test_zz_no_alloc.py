@@ -13,6 +13,7 @@ import torch
 
 import ae296_b200 as L
 from lora_testlib import TOL
+from oracle import lora_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -32,17 +33,35 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
     for seed, t, n, h_in, h_out, r, dtype in cases:        # two calls in a row, different shapes
         x, wa, wb, ids, y0 = _inputs(seed, t, n, h_in, h_out, r, dtype)
         want = y0.clone()
-        L.add_lora_bgmv(want, x, wa, wb, ids, 1, 0.5)
+        ws = torch.empty(L.add_lora_bgmv_workspace_bytes(t, n, h_in), dtype=torch.uint8, device="cuda")
+        L.add_lora_bgmv_once(want, x, wa, wb, ids, 1, 0.5, ws)          # b200_add_lora_bgmv, caller's workspace
         got = y0.clone()
         before = torch.cuda.memory_allocated()
         L.add_lora_bgmv_static(got, x, wa, wb, ids, 1, 0.5)
         assert torch.cuda.memory_allocated() == before, "the static entry point must not allocate"
         torch.cuda.synchronize()
-        delta = (want.float() - y0.float())
-        rms = float(delta.pow(2).mean().sqrt())
-        assert float((got.float() - want.float()).abs().max()) <= TOL * rms
+        L.add_lora_bgmv_static_status()
+        # same kernels, same launch geometry, same summation order: the same bits
+        assert torch.equal(got, want)
+        # and the answer itself, against the float64 oracle: y0 + 0.5 * delta rounded once
+        idn = ids.cpu().numpy()
+        d = O.lora_delta(x.double().cpu().numpy(), lambda a: wa[a, 1].double().cpu().numpy(),
+                         lambda a: wb[a, 1].double().cpu().numpy(), idn, np.full(n, 0.5))
+        exact = y0.double().cpu().numpy() + d
+        ulp = 2.0 ** (-10 if dtype == torch.float16 else -7)
+        assert np.abs(got.double().cpu().numpy() - exact).max() <= TOL * np.sqrt((d ** 2).mean()) + ulp * np.abs(exact).max()
     # a call beyond the stated limits is refused, not attempted
     x, wa, wb, ids, y0 = _inputs(303, 65, 4, 256, 256, 8, torch.float16)
     with pytest.raises(L.LoraError) as e:
         L.add_lora_bgmv_static(y0.clone(), x, wa, wb, ids, 0, 1.0)
     assert e.value.code == -6
+    # an adapter id outside the pool: y stays as it was and the status call says why
+    x, wa, wb, ids, y0 = _inputs(404, 16, 4, 256, 256, 8, torch.float16)
+    ids[5] = 4
+    y = y0.clone()
+    L.add_lora_bgmv_static(y, x, wa, wb, ids, 0, 1.0)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y0)
+    with pytest.raises(L.LoraError) as e:
+        L.add_lora_bgmv_static_status()
+    assert e.value.code == -8
