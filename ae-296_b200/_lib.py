@@ -12,7 +12,7 @@ import os
 from .build import LIB_PATH
 
 F16, BF16, F32 = 0, 1, 2
-MID_ROUND, NO_TENSOR, ONLY_SHRINK, ONLY_EXPAND, DELTA_THEN_ADD = 1, 2, 4, 8, 32
+MID_ROUND, NO_TENSOR, ONLY_SHRINK, ONLY_EXPAND, DELTA_THEN_ADD, KEEP_PARTIALS = 1, 2, 4, 8, 32, 64
 MAX_RANK, MAX_PROJ = 64, 4
 
 STATUS = {
@@ -46,6 +46,7 @@ class Proj(C.Structure):
 SYMBOLS = {
     "b200_lora_arch": (C.c_int, []),
     "b200_lora_last_cuda_error": (C.c_char_p, []),
+    "b200_lora_stream_capture_id": (C.c_int, [C.c_void_p, C.POINTER(C.c_ulonglong)]),
     "b200_lora_plan_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "b200_lora_plan_build": (C.c_int, [C.c_void_p, C.c_size_t, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                        C.POINTER(Adapters), C.c_void_p]),

@@ -164,6 +164,16 @@ int b200_lora_arch(void) { return 100; }
 
 const char* b200_lora_last_cuda_error(void) { return g_last_error; }
 
+int b200_lora_stream_capture_id(void* stream, unsigned long long* id) {
+    if (!id) return B200_LORA_ERR_NULL;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    unsigned long long cid = 0;
+    cudaError_t e = cudaStreamGetCaptureInfo(static_cast<cudaStream_t>(stream), &st, &cid);
+    if (e != cudaSuccess) return cuda_fail(e);
+    *id = st == cudaStreamCaptureStatusActive ? cid : 0ull;
+    return B200_LORA_OK;
+}
+
 size_t b200_lora_plan_bytes(int32_t max_tokens, int32_t n_adapters) {
     if (max_tokens < 1 || n_adapters < 1) return 0;
     return plan_words(max_tokens, n_adapters) * 4;
@@ -313,7 +323,9 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     }
     bool fast = fast_ranks(adapters);
     for (int i = 0; i < n_proj; ++i)
-        if ((projs[i].h_in % 256) || (projs[i].h_out % 256) || projs[i].h_in > 8192) fast = false;
+        // units are cut at multiples of 128 columns (the shrink kernel's weight box, the widest
+        // per-warp column group of the expand kernel), so the last unit of a row may be partial
+        if ((projs[i].h_in % 128) || (projs[i].h_out % 128) || projs[i].h_in > 8192) fast = false;
     if (fast) {
         for (int i = 0; i < n_proj && fast; ++i)
             for (int c = 0; c < 4 && fast; ++c) {

@@ -493,8 +493,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
             const int s = n % kStages;
             const unsigned ph = (n / kStages) & 1;
             const Item it = make_item(p, rec, cur, false);
-            mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 1);
+            // There are twice as many meta slots as stages, so unit n's slot is free once unit
+            // n - kStages has been handed over: fill it before waiting for the stage itself, and
+            // nothing but the copies stands between that wait and the stage being in flight again.
             publish_meta(&meta[n % kMetaSlots], rec, it, lane);
+            mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 1);
             const unsigned full = smem_u32(&bars[s]);
             if (it.valid) shrink_produce<T>(p, it, rec, smem_u32(smem + s * kShrinkStage), full, lane, waited ? 3 : 1);
             else if (lane == 0) mbar_arrive(full);
@@ -632,9 +635,12 @@ __device__ __forceinline__ unsigned hl_pack(float v0, float v1, bool lo) {
 //   R=64: chunks 2t and 2t+1 of each 128-byte weight row (4 MMA k-steps)
 //   R=32: chunk t of each 64-byte row (2 k-steps);  R=16: 8 bytes (1 k-step);  R=8: 4 bytes.
 // A warp owns NBW consecutive 16-column blocks; the consumer warps never meet at a barrier.
+// A warp first moves everything it needs of the stage into registers (intermediate fragments,
+// weight fragments, the staged y values), hands the stage back (`empty_bar`) and only then
+// computes: the time a stage stays out of flight does not include the arithmetic.
 template <typename T, int R>
 __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta& m, const int* tok_rows, unsigned char* stage,
-                                               int tid, unsigned (&bf)[2][4][2], bool reuse) {
+                                               int tid, unsigned (&bf)[2][4][2], bool reuse, unsigned empty_bar) {
     constexpr int KS = R == 64 ? 4 : R == 32 ? 2 : 1;
     constexpr int JC = kSuper / (R <= 16 ? 4 : R / 4);
     constexpr int NBW = JC / 16 / kConsWarps;              // 16-column blocks per warp: 4, 4, 2, 1
@@ -686,118 +692,112 @@ __device__ __forceinline__ void expand_consume(const ApplyParams& p, const Meta&
     }
 
     const int jbase = warp * NBW * 16;
-    float acc[NBW][2][4];
+    // the weight fragments of all of the warp's blocks
+    unsigned a[NBW][KS][4];
 #pragma unroll
     for (int nb = 0; nb < NBW; ++nb) {
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) acc[nb][grp][0] = acc[nb][grp][1] = acc[nb][grp][2] = acc[nb][grp][3] = 0.f;
         const unsigned char* w0 = stage + (jbase + nb * 16 + g) * (R * 2);   // output column g of the block
         const unsigned char* w1 = w0 + 8 * (R * 2);                          // output column g + 8
-        unsigned a[KS][4];
         if constexpr (R == 64) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const uint4 r0 = *reinterpret_cast<const uint4*>(w0 + (2 * t + c) * 16);
                 const uint4 r1 = *reinterpret_cast<const uint4*>(w1 + (2 * t + c) * 16);
-                a[2 * c][0] = r0.x; a[2 * c][1] = r1.x; a[2 * c][2] = r0.y; a[2 * c][3] = r1.y;
-                a[2 * c + 1][0] = r0.z; a[2 * c + 1][1] = r1.z; a[2 * c + 1][2] = r0.w; a[2 * c + 1][3] = r1.w;
+                a[nb][2 * c][0] = r0.x; a[nb][2 * c][1] = r1.x; a[nb][2 * c][2] = r0.y; a[nb][2 * c][3] = r1.y;
+                a[nb][2 * c + 1][0] = r0.z; a[nb][2 * c + 1][1] = r1.z; a[nb][2 * c + 1][2] = r0.w; a[nb][2 * c + 1][3] = r1.w;
             }
         } else if constexpr (R == 32) {
             const uint4 r0 = *reinterpret_cast<const uint4*>(w0 + t * 16);
             const uint4 r1 = *reinterpret_cast<const uint4*>(w1 + t * 16);
-            a[0][0] = r0.x; a[0][1] = r1.x; a[0][2] = r0.y; a[0][3] = r1.y;
-            a[1][0] = r0.z; a[1][1] = r1.z; a[1][2] = r0.w; a[1][3] = r1.w;
+            a[nb][0][0] = r0.x; a[nb][0][1] = r1.x; a[nb][0][2] = r0.y; a[nb][0][3] = r1.y;
+            a[nb][1][0] = r0.z; a[nb][1][1] = r1.z; a[nb][1][2] = r0.w; a[nb][1][3] = r1.w;
         } else if constexpr (R == 16) {
             const uint2 r0 = *reinterpret_cast<const uint2*>(w0 + t * 8);
             const uint2 r1 = *reinterpret_cast<const uint2*>(w1 + t * 8);
-            a[0][0] = r0.x; a[0][1] = r1.x; a[0][2] = r0.y; a[0][3] = r1.y;
+            a[nb][0][0] = r0.x; a[nb][0][1] = r1.x; a[nb][0][2] = r0.y; a[nb][0][3] = r1.y;
         } else {
-            a[0][0] = *reinterpret_cast<const unsigned*>(w0 + t * 4);
-            a[0][1] = *reinterpret_cast<const unsigned*>(w1 + t * 4);
-            a[0][2] = a[0][3] = 0u;
-        }
-#pragma unroll
-        for (int k = 0; k < KS; ++k) Mma<T>::run(acc[nb][0], a[k][0], a[k][1], a[k][2], a[k][3], bf[0][k][0], bf[0][k][1]);
-        if (ngrp == 2) {
-#pragma unroll
-            for (int k = 0; k < KS; ++k) Mma<T>::run(acc[nb][1], a[k][0], a[k][1], a[k][2], a[k][3], bf[1][k][0], bf[1][k][1]);
+            a[nb][0][0] = *reinterpret_cast<const unsigned*>(w0 + t * 4);
+            a[nb][0][1] = *reinterpret_cast<const unsigned*>(w1 + t * 4);
+            a[nb][0][2] = a[nb][0][3] = 0u;
         }
     }
-
     // Token t (+4): hi + lo products for columns g and g + 8.  Lanes g and g ^ 1 swap one value
     // so that each ends up with two adjacent columns: (g, g+1) for even g, (g+7, g+8) for odd g.
-    unsigned char* ysb = stage + kWTile;
+    const unsigned char* ysb = stage + kWTile;
     constexpr int ypitch = JC * 2 + kYPad;
     const bool staged = !(p.y_f32 || (p.flags & B200_LORA_DELTA_THEN_ADD));
     const int jl = jbase + (lo_half ? g + 7 : g);
-    float d0[NBW][2], d1[NBW][2];
+    const bool col_ok = jbase < m.width_ok;                // the warp's columns lie inside the matrix
+    // the staged y values this lane will update, and the rows they go back to
+    unsigned yw[2][NBW];
+    int row[2];
 #pragma unroll
-    for (int nb = 0; nb < NBW; ++nb) {
+    for (int grp = 0; grp < 2; ++grp) {
+        const int q = t + 4 * grp;
+        row[grp] = (grp < ngrp && q < ntok && col_ok) ? tok_rows[q] : -1;
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-            d0[nb][grp] = d1[nb][grp] = 0.f;
-            if (grp < ngrp) {
-                const float c_lo = scale * (acc[nb][grp][0] + acc[nb][grp][1]);
-                const float c_hi = scale * (acc[nb][grp][2] + acc[nb][grp][3]);
-                const float got = __shfl_xor_sync(0xffffffffu, lo_half ? c_lo : c_hi, 4);
-                d0[nb][grp] = lo_half ? got : c_lo;
-                d1[nb][grp] = lo_half ? c_hi : got;
-            }
+        for (int nb = 0; nb < NBW; ++nb) yw[grp][nb] = 0u;
+        if (staged && row[grp] >= 0) {
+            const unsigned* ys = reinterpret_cast<const unsigned*>(ysb + q * ypitch + jl * 2);
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) yw[grp][nb] = ys[nb * 8];
         }
     }
-    const bool col_ok = jbase < m.width_ok;                // the warp's columns lie inside the matrix
-    if (staged) {
-        // the staged y tile is only read: every lane adds its pairs and stores them straight to
-        // global memory, eight lanes filling one 32-byte sector of a token's row
+    // the stage is no longer needed
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar);
+
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-            const int q = t + 4 * grp;
-            if (grp < ngrp && q < ntok && col_ok) {
-                const unsigned* ys = reinterpret_cast<const unsigned*>(ysb + q * ypitch + jl * 2);
-                unsigned* yg = reinterpret_cast<unsigned*>(reinterpret_cast<T*>(pj.y) + (long long)tok_rows[q] * pj.ldy + m.c0 + jl);
-                unsigned yw[NBW];
+    for (int grp = 0; grp < 2; ++grp) {
+        if (grp >= ngrp) break;                            // uniform across the warp
+        float d0[NBW], d1[NBW];
 #pragma unroll
-                for (int nb = 0; nb < NBW; ++nb) yw[nb] = ys[nb * 8];
+        for (int nb = 0; nb < NBW; ++nb) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int nb = 0; nb < NBW; ++nb) {
-                    float lo, hi;
-                    if (Cvt<T>::is_bf16) {
-                        lo = __uint_as_float(yw[nb] << 16); hi = __uint_as_float(yw[nb] & 0xffff0000u);
-                    } else {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&yw[nb]));
-                        lo = f.x; hi = f.y;
-                    }
-                    yg[nb * 8] = Cvt<T>::pack2(lo + d0[nb][grp], hi + d1[nb][grp]);
-                }
-            }
+            for (int k = 0; k < KS; ++k) Mma<T>::run(acc, a[nb][k][0], a[nb][k][1], a[nb][k][2], a[nb][k][3], bf[grp][k][0], bf[grp][k][1]);
+            const float c_lo = scale * (acc[0] + acc[1]);
+            const float c_hi = scale * (acc[2] + acc[3]);
+            const float got = __shfl_xor_sync(0xffffffffu, lo_half ? c_lo : c_hi, 4);
+            d0[nb] = lo_half ? got : c_lo;
+            d1[nb] = lo_half ? c_hi : got;
         }
-    } else {
+        if (row[grp] < 0) continue;
+        const long long yoff = (long long)row[grp] * pj.ldy + m.c0 + jl;
+        if (staged) {
+            // every lane adds its pairs and stores them straight to global memory, eight lanes
+            // filling one 32-byte sector of a token's row
+            unsigned* yg = reinterpret_cast<unsigned*>(reinterpret_cast<T*>(pj.y) + yoff);
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-            const int q = t + 4 * grp;
-            if (grp < ngrp && q < ntok && col_ok) {
-                const long long yoff = (long long)tok_rows[q] * pj.ldy + m.c0 + jl;
-                if (p.y_f32) {
-                    float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + yoff);
-                    float2 yv[NBW];
-#pragma unroll
-                    for (int nb = 0; nb < NBW; ++nb) yv[nb] = yp[nb * 8];
-#pragma unroll
-                    for (int nb = 0; nb < NBW; ++nb) {
-                        yv[nb].x += d0[nb][grp]; yv[nb].y += d1[nb][grp];
-                        yp[nb * 8] = yv[nb];
-                    }
+            for (int nb = 0; nb < NBW; ++nb) {
+                float lo, hi;
+                if (Cvt<T>::is_bf16) {
+                    lo = __uint_as_float(yw[grp][nb] << 16); hi = __uint_as_float(yw[grp][nb] & 0xffff0000u);
                 } else {
-                    // the delta is rounded to the I/O type and added to y in that type, two outputs
-                    // per reduction, straight in global memory: no y tile, no write-back
-                    T* yp = reinterpret_cast<T*>(pj.y) + yoff;
-#pragma unroll
-                    for (int nb = 0; nb < NBW; ++nb) {
-                        const unsigned d = Cvt<T>::pack2(d0[nb][grp], d1[nb][grp]);
-                        if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
-                        else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
-                    }
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&yw[grp][nb]));
+                    lo = f.x; hi = f.y;
                 }
+                yg[nb * 8] = Cvt<T>::pack2(lo + d0[nb], hi + d1[nb]);
+            }
+        } else if (p.y_f32) {
+            float2* yp = reinterpret_cast<float2*>(reinterpret_cast<float*>(pj.y) + yoff);
+            float2 yv[NBW];
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) yv[nb] = yp[nb * 8];
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) {
+                yv[nb].x += d0[nb]; yv[nb].y += d1[nb];
+                yp[nb * 8] = yv[nb];
+            }
+        } else {
+            // the delta is rounded to the I/O type and added to y in that type, two outputs
+            // per reduction, straight in global memory: no y tile, no write-back
+            T* yp = reinterpret_cast<T*>(pj.y) + yoff;
+#pragma unroll
+            for (int nb = 0; nb < NBW; ++nb) {
+                const unsigned d = Cvt<T>::pack2(d0[nb], d1[nb]);
+                if (Cvt<T>::is_bf16) asm volatile("red.global.add.noftz.bf16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
+                else asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(yp + nb * 16), "r"(d) : "memory");
             }
         }
     }
@@ -864,12 +864,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             // ... except the CTA's very first unit, whose intermediate the (still idle) consumer
             // warps add up with all their threads: it is on the kernel's critical path
             const bool by_consumers = n == 0 && fc.n_units != 0;
-            mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
-            Meta* slot = &meta[n % kMetaSlots];
+            Meta* slot = &meta[n % kMetaSlots];          // free already (see the shrink kernel)
             publish_meta(slot, rec, it, lane);
             if (lane == 0) { slot->pad[0] = (need_v && !by_consumers) ? 1 : 0; slot->pad[1] = cur.unit; }
             __syncwarp();
             if (n == 0) asm volatile("bar.arrive 2, %0;" ::"n"(kConsThreads + 32) : "memory");   // meta slot 0 is published
+            mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
             const unsigned full = smem_u32(&bars[s]);
             if (it.valid) expand_produce<T>(p, ws, it, rec, smem + s * kExpandStage, full, lane, waited ? 7 : 1, need_v && !by_consumers, fc, cur.unit);
             else if (lane == 0) mbar_arrive(full);
@@ -913,15 +913,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             const int key = m.proj * p.cap + m.u.wseg;
             const bool reuse = key == bf_key;
             bf_key = key;
+            const unsigned empty_bar = smem_u32(&bars[kStages + s]);      // one arrival per consumer warp, made inside
             switch (m.u.rank) {
-                case 8:  expand_consume<T, 8>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse); break;
-                case 16: expand_consume<T, 16>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse); break;
-                case 32: expand_consume<T, 32>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse); break;
-                default: expand_consume<T, 64>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse); break;
+                case 8:  expand_consume<T, 8>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse, empty_bar); break;
+                case 16: expand_consume<T, 16>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse, empty_bar); break;
+                case 32: expand_consume<T, 32>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse, empty_bar); break;
+                default: expand_consume<T, 64>(p, m, meta[n % kMetaSlots].u.tok, stage, tid, bf, reuse, empty_bar); break;
             }
+        } else {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars[kStages + s]));     // one arrival per consumer warp
     }
 }
 
@@ -982,7 +984,7 @@ cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
     cudaError_t e = cudaSuccess;
     if (!(p.flags & B200_LORA_ONLY_EXPAND)) {
         e = launch_pdl(bgmv_shrink_tma_kernel<T>, grid, kThreads, kShrinkSmem, s, p);
-        if (e == cudaSuccess && (p.flags & B200_LORA_ONLY_SHRINK))
+        if (e == cudaSuccess && (p.flags & B200_LORA_ONLY_SHRINK) && !(p.flags & B200_LORA_KEEP_PARTIALS))
             e = launch_pdl(fold_partials_kernel<T>, dim3(n_sm, p.n_proj), 128, 0, s, p, grid);
     }
     if (e == cudaSuccess && !(p.flags & B200_LORA_ONLY_SHRINK))

@@ -198,8 +198,10 @@ def _plan_for(ids: torch.Tensor, t: int, n: int, r: int, h_in: int, scale: float
     The reference's decode loop calls the op 3 x n_layers times per step with the SAME index tensor
     (lightllm/models/lora_gpu.py:138,150,162 with ``select_inds[bsz-1]``).  The plan depends on
     the ids, N, r and the scale only, so it is kept while the very same tensor object is passed
-    again unmodified (torch's version counter) and rebuilt otherwise.  During CUDA-graph capture
-    it is always rebuilt inside the graph, because a replay does not come back here."""
+    again unmodified (torch's version counter) and rebuilt otherwise.  A plan built outside a
+    CUDA-graph capture is never used inside one, nor one capture's plan in another: the capture's
+    identifier is part of the key, so every graph contains the build of the plan it applies (its
+    first call) and replays rebuild it from the index tensor's contents of the moment."""
     dev = ids.device
     skey = (dev.index, _stream(dev))
     st = _OP_STATE.get(skey)
@@ -209,13 +211,14 @@ def _plan_for(ids: torch.Tensor, t: int, n: int, r: int, h_in: int, scale: float
         st.dims = (max(t, st.dims[0]), max(n, st.dims[1]), max(h_in, st.dims[2]))
         st.batch = LoraBatch(st.dims[0], st.dims[1], st.dims[2], 1, dev)
         st.key = None
-    key = (ids.data_ptr(), ids._version, ids.dtype, t, n, r, float(scale))
-    capturing = torch.cuda.is_current_stream_capturing()
-    same = (not capturing and st.key == key and st.ids_ref is not None and st.ids_ref() is ids)
+    cap = C.c_ulonglong(0)
+    check(_lib.lib().b200_lora_stream_capture_id(_stream(dev), C.byref(cap)), "stream_capture_id")
+    key = (ids.data_ptr(), ids._version, ids.dtype, t, n, r, float(scale), cap.value)
+    same = st.key == key and st.ids_ref is not None and st.ids_ref() is ids
     if not same:
         st.batch.plan.build(ids, ad)
-        st.key = None if capturing else key
-        st.ids_ref = None if capturing else weakref.ref(ids)
+        st.key = key
+        st.ids_ref = weakref.ref(ids)
     return st.batch
 
 

@@ -53,6 +53,9 @@ enum {
     B200_LORA_ONLY_SHRINK = 4, /* tensor parallel: run only the shrink half; the intermediate v is left in the
                                   workspace (b200_lora_workspace_v_region) for the caller to sum over ranks */
     B200_LORA_ONLY_EXPAND = 8, /* tensor parallel: run only the expand half on the workspace's current v */
+    B200_LORA_KEEP_PARTIALS = 64, /* with B200_LORA_ONLY_SHRINK on the TMA kernels: leave the split-K partial sums
+                                   as they are instead of adding them up into v (a caller that reduces them
+                                   itself, or that times the shrink kernel alone) */
     B200_LORA_DELTA_THEN_ADD = 32 /* 16-bit y only: round the delta to the I/O type and add it to y in that
                                    type, as the reference's `q += q_lora` does
                                    (lightllm/models/llama/layer_infer/transformer_layer_infer.py:160-170).
@@ -95,6 +98,11 @@ typedef struct b200_lora_proj {
 int b200_lora_arch(void);
 /* Text of the last CUDA error this thread's calls observed ("" if none). */
 const char* b200_lora_last_cuda_error(void);
+/* *id = the identifier of the CUDA-graph capture `stream` is part of, 0 when it is not capturing.
+ * Host code that keeps a plan between calls (the reference's loop passes the same index tensor
+ * 3 x n_layers times, lightllm/models/lora_gpu.py:138,150,162) uses it to keep a plan only within
+ * one capture: a graph must contain the build of every plan it applies. */
+int b200_lora_stream_capture_id(void* stream, unsigned long long* id);
 
 /* ---- plan: adapter-index gather and segment bookkeeping -----------------------------
  * The plan is a device-resident table built from the per-token adapter ids: a stable

@@ -76,11 +76,13 @@ def test_prefill_7b_full_size_three_projections_one_apply():
 @pytest.mark.parametrize("name,h_in,h_outs,ranks,dtype,T,N,zipf", [
     ("13b-tp8", 5120, (5120, 5120, 5120), [16, 32, 64], "bf16", 96, 40, 1.0),      # shards 640 -> 640
     ("70b-tp8-qkv", 8192, (8192, 1024, 1024), 64, "bf16", 64, 24, 1.2),            # shards 1024 -> 1024 | 128 | 128
+    ("odd-widths", 2560, (2560, 320 * 8, 192 * 8), [16, 32, 64], "fp16", 70, 20, 1.0),   # shards 320 -> 320 | 320 | 192: general kernels
 ])
 def test_eight_way_shards_shrink_sum_expand(name, h_in, h_outs, ranks, dtype, T, N, zipf):
     """The shard widths of eight-way tensor parallelism (A cut along the hidden dimension, B along
     the output), run rank after rank on one GPU: shrink halves, the sum NCCL would form, expand
-    halves.  640 and 128 are not multiples of 256."""
+    halves.  640 and 128 are whole 128-column blocks (the TMA kernels take them); 320 and 192 are not
+    (the general kernels' two halves)."""
     tp = 8
     rng = np.random.default_rng(5)
     p = 1.0 / np.arange(1, N + 1) ** zipf
