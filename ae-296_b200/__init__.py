@@ -12,3 +12,5 @@ from .ops import (LoraBatch, LoraPlan, LoraWorkspace, add_lora_bgmv, add_lora_bg
                   add_lora_bgmv_workspace_bytes, adapters_of, apply, invalidate_plan_cache)
 from . import ops                                            # noqa: F401
 from .lora_gpu import Lora_GPU                               # noqa: F401
+from .lora_cpu import Lora_CPU, ShmSegments                  # noqa: F401
+from .placement import place_by_adapter                      # noqa: F401

@@ -42,7 +42,7 @@ class Proj(C.Structure):
                 ("ldx", C.c_int64), ("ldy", C.c_int64), ("h_in", C.c_int32), ("h_out", C.c_int32)]
 
 
-# name -> (restype, argtypes); every symbol include/b200_lora.h declares
+# name -> (restype, argtypes); every symbol the headers under include/ declare
 SYMBOLS = {
     "b200_lora_arch": (C.c_int, []),
     "b200_lora_last_cuda_error": (C.c_char_p, []),
@@ -69,6 +69,20 @@ SYMBOLS = {
                                             C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_int32, C.c_float, C.c_int32, C.c_void_p]),
     "b200_add_lora_bgmv_static_status": (C.c_int, [C.c_void_p]),
+    # include/b200_cpu_assist.h
+    "b200_xfer_register_pinned": (C.c_int, [C.c_void_p, C.c_size_t]),
+    "b200_xfer_unregister_pinned": (C.c_int, [C.c_void_p]),
+    "b200_xfer_d2h_async": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200_xfer_signal_d2h_async": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "b200_xfer_d2h_with_signal_async": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t,
+                                                  C.c_void_p, C.c_void_p]),
+    "b200_xfer_h2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "b200_xfer_h2d_2d_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                         C.c_size_t, C.c_void_p]),
+    "b200_xfer_stream_synchronize": (C.c_int, [C.c_void_p]),
+    "b200_cpu_assist_invoke": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
+    "b200_cpu_assist_collect_qkv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                              C.c_int64, C.POINTER(C.c_int32), C.c_void_p]),
 }
 
 _LIB = None

@@ -567,6 +567,8 @@ def main():
     dev = torch.device("cuda", local)
     numa = numa_pin(local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"           # keeps NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     base = make_workload(args.workload)

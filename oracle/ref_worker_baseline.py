@@ -77,6 +77,7 @@ class ReferenceWorkerPool:
         for name in SEGMENTS:
             self._make(name, nbytes)
         self._make("shm_tkn_len", 8)
+        self._make("lock", 8)                       # layer hand-shake of the host side (create_shm.py), unused by workers
         n_workers = len(ranks_of_worker)
         self._make("shm_signal", 2 * max(n_workers, 1))
         self.arr = {n: np.ndarray((ROWS_MAX, max_len, hidden), np.float16, buffer=self.shms[n].buf) for n in SEGMENTS}
