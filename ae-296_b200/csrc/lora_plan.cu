@@ -200,7 +200,7 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem, const
                     for (int c = 0; c < ch; ++c) {
                         pv.ws_start[w] = pb + min(c * per, len);
                         pv.ws_adapter[w] = a;
-                        pv.ws_rank[w] = r;
+                        pv.ws_rank[w] = r | (kind << 16);
                         pv.ws_unit0[w] = u;
                         u += nsub;
                         ++w;
@@ -226,10 +226,44 @@ __device__ void build_units(PlanView pv, const PlanAdapters ad, int* smem, const
         pv.hdr->n_tiles = tot_tiles;
     }
     __syncthreads();
+    // Where a work segment's units sit in the unit list is free (every record names its own segment).
+    // Segments come out of the walk above adapter by adapter, so a popular adapter's many full
+    // 8-token segments - the expensive units - would be neighbours and land in the ranges of a few
+    // CTAs.  Deal the list positions out with a stride near the golden section of the segment count
+    // instead (coprime with it, so every segment gets one position): any window of the list then
+    // holds a fair sample of cheap and expensive units.  Short stretches keep coming first.
+    if (tot_ws > 2) {
+        if (tid == 0) {
+            int stride = (int)(tot_ws * 0.6180339887f) | 1;
+            auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
+            while (gcd(stride, tot_ws) != 1) stride += 2;
+            smem[41] = stride;
+        }
+        __syncthreads();
+        const int stride = smem[41];
+        for (int kind = 0; kind < 2; ++kind) {
+            int carry = kind ? tot_short : 0;
+            for (int base = 0; base < tot_ws; base += kPlanThreads) {
+                const int i = base + tid;
+                int w = -1, val = 0;
+                if (i < tot_ws) {
+                    w = (int)(((long long)i * stride) % tot_ws);
+                    const int rk = pv.ws_rank[w];
+                    if ((rk >> 16) == kind) val = n_sub(pad_rank(rk & 0xffff));
+                    else w = -1;
+                }
+                int tot;
+                const int off = block_scan_excl(val, tot, warp_sums);
+                if (w >= 0) pv.ws_unit0[w] = carry + off;
+                carry += tot;
+            }
+        }
+        __syncthreads();
+    }
     // unit records: one work segment per thread, n_sub records of four 16-byte stores each
     for (int w = tid; w < tot_ws; w += kPlanThreads) {
         const int cb = pv.ws_start[w], ce = pv.ws_start[w + 1];
-        const int a = pv.ws_adapter[w], r = pv.ws_rank[w];
+        const int a = pv.ws_adapter[w], r = pv.ws_rank[w] & 0xffff;
         const int nsub = n_sub(pad_rank(r));
         const long long cum = cum_ranks ? cum_ranks[a] : 0;
         UnitRec rec;
