@@ -258,8 +258,8 @@ __device__ __forceinline__ void shrink_fold(const ApplyParams& p, const Workspac
 
 template <typename T>
 __global__ void __launch_bounds__(kCtaThreads, 1) bgmv_shrink_kernel(const __grid_constant__ ApplyParams p) {
-    pdl_launch_dependents();
     pdl_wait_prior();
+    pdl_launch_dependents();            // only after the wait: see lora_common.cuh
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* stages = smem;
     float* red = reinterpret_cast<float*>(smem + kStages * kShrinkStage);   // 8 or 16 slices x 8 tokens x (r_pad + 4)
@@ -511,8 +511,8 @@ __device__ __forceinline__ void expand_compute(const ApplyParams& p, const Meta&
 
 template <typename T>
 __global__ void __launch_bounds__(kCtaThreads, 1) bgmv_expand_kernel(const __grid_constant__ ApplyParams p) {
-    pdl_launch_dependents();
     pdl_wait_prior();
+    pdl_launch_dependents();            // only after the wait: see lora_common.cuh
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* stages = smem;
     Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kExpandStage);

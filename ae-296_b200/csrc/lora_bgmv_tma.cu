@@ -442,7 +442,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kShrinkStage + 2 * kRedBytes);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
 
-    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -455,7 +454,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_shrink_tma_kernel(c
     // The consumers wait for the predecessor kernel here.  The producers read only the plan and
     // the weight pools at first, which no kernel that may still be running writes, and wait
     // before they touch x: the first weight copies overlap the predecessor's tail.
-    if (warp < kConsWarps) pdl_wait_prior();
+    if (warp < kConsWarps) {
+        pdl_wait_prior();
+        if (tid == 0) pdl_launch_dependents();
+    }
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -548,7 +550,8 @@ struct FoldCtx {
 
 // `parts` bit 0: the barrier's byte count and the weight tile (never written while kernels of
 // this library run, so they may be requested before the predecessor kernel has ended); bit 2:
-// the y rows; bit 1, always last: the intermediate v and the producer's arrival.  v is needed
+// the y rows (final once the kernel before the predecessor has completed); bit 1, always last:
+// the intermediate v and the producer's arrival.  v is needed
 // only by the first unit a CTA has of a (projection, work segment) - the consumers keep its
 // fragments for the units that follow - and comes either from the workspace (a tensor-parallel
 // caller has summed it over the ranks) or from the shrink kernel's split-K slots, which the
@@ -809,7 +812,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
     Meta* meta = reinterpret_cast<Meta*>(smem + kStages * kExpandStage);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(meta + kMetaSlots);
 
-    pdl_launch_dependents();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -819,7 +821,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp < kConsWarps) pdl_wait_prior();               // the producers wait before they touch y or v
+    if (warp < kConsWarps) {                               // the producers wait before they touch v
+        pdl_wait_prior();
+        if (tid == 0) pdl_launch_dependents();
+    }
 
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
@@ -842,8 +847,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
         fc.n_units = (p.flags & B200_LORA_ONLY_EXPAND) ? 0 : n_units;
         fc.per_cta = (n_units * p.total_super_in + (int)gridDim.x - 1) / (int)gridDim.x;
         bool waited = false;
-        // after the wait: y and v of the units whose weights were requested before it; the meta
-        // slot's spare words hold what that takes (first unit of the segment, does it need v)
+        // Before the wait: weights and y rows (when this CTA runs, every kernel before the
+        // predecessor has completed - see the note on programmatic launches in lora_common.cuh -
+        // and the predecessor, this apply's shrink or reduction step, does not write y).  After
+        // the wait: the intermediates of those units; the meta slot's spare words hold what that
+        // takes (first unit of the segment, does it need v)
         auto late_parts = [&](int upto) {
             pdl_wait_prior();
             waited = true;
@@ -851,7 +859,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
                 const Meta& mk = meta[k % kMetaSlots];
                 if (mk.valid)
                     expand_produce<T>(p, ws, item_of_meta(mk), record_of_meta(mk, lane), smem + (k % kStages) * kExpandStage,
-                                      smem_u32(&bars[k % kStages]), lane, 2 | 4, mk.pad[0] != 0, fc, mk.pad[1]);
+                                      smem_u32(&bars[k % kStages]), lane, 2, mk.pad[0] != 0, fc, mk.pad[1]);
             }
         };
         for (int n = pw; n < n_local; n += kProdWarps) {
@@ -871,7 +879,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
             if (n == 0) asm volatile("bar.arrive 2, %0;" ::"n"(kConsThreads + 32) : "memory");   // meta slot 0 is published
             mbar_wait(smem_u32(&bars[kStages + s]), ph ^ 1, err, 3);
             const unsigned full = smem_u32(&bars[s]);
-            if (it.valid) expand_produce<T>(p, ws, it, rec, smem + s * kExpandStage, full, lane, waited ? 7 : 1, need_v && !by_consumers, fc, cur.unit);
+            if (it.valid) expand_produce<T>(p, ws, it, rec, smem + s * kExpandStage, full, lane, waited ? 7 : 1 | 4, need_v && !by_consumers, fc, cur.unit);
             else if (lane == 0) mbar_arrive(full);
             if (n + kProdWarps < n_local) cursor_advance(p, n_units, true, pv.unit_tab, lane, kProdWarps, cur, rec);
         }
@@ -931,8 +939,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) bgmv_expand_tma_kernel(c
 // adds up the split-K slots of every (projection, work segment) into v in the workspace.
 template <typename T>
 __global__ void __launch_bounds__(128) fold_partials_kernel(const __grid_constant__ ApplyParams p, int shrink_grid) {
-    pdl_launch_dependents();
     pdl_wait_prior();
+    pdl_launch_dependents();
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;

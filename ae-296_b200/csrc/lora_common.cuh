@@ -251,10 +251,16 @@ __device__ __forceinline__ uint4 ldg_nc16(const void* p) {
 __device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // ---- programmatic dependent launch -----------------------------------------------------------
-// Every kernel of this library lets its successor in the stream start launching at once and
-// waits for its predecessor's memory only after its own on-chip set-up, so launch latency and
-// prologue overlap the previous kernel's tail.  Both instructions are no-ops without the
-// launch attribute.
+// Kernels of this library are launched with programmatic stream serialisation, so a kernel's CTAs
+// may start while its predecessor in the stream still runs, and use that to set up and to request
+// data that the predecessor does not write.  Two rules keep this safe for chains of any length:
+//   1. every CTA waits for the predecessor (griddepcontrol.wait by at least one thread) before it
+//      exits, idle CTAs included, so that a kernel's completion implies its predecessor's;
+//   2. a CTA lets the successor launch (griddepcontrol.launch_dependents) only after that wait.
+// By induction, when any CTA of a kernel runs, every kernel before its predecessor has completed:
+// what those wrote (the activations, the y an earlier apply accumulated into) may be read at once,
+// and only what the predecessor itself writes has to wait.  Both instructions are no-ops without
+// the launch attribute.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -184,7 +184,6 @@ __device__ __forceinline__ TileInfo tile_info(const SgmvParams& sp, const ApplyP
 template <typename T>
 __global__ void __launch_bounds__(kSgmvThreads, 1)
 sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ SgmvParams sp) {
-    pdl_launch_dependents();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // tensor-parallel callers, and the launcher when tiles are few, run the two halves separately
@@ -209,7 +208,10 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const int D2_FULL = D1_FULL + 6, D2_EMPTY = D1_FULL + 8, Y_FULL = D1_FULL + 10, Y_DONE = Y_FULL + kYSMax;
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
 
-    if (!(p.flags & kFlagLateWait)) pdl_wait_prior();
+    if (!(p.flags & kFlagLateWait)) {
+        pdl_wait_prior();
+        if (threadIdx.x == 0) pdl_launch_dependents();
+    }
     PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
     WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
     const PlanHeader hdr = *pv.hdr;
@@ -499,7 +501,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                     continue;
                 }
             } else {                                         // expand half only: v was summed by the caller
-                if (p.flags & kFlagLateWait) pdl_wait_prior();
+                if (p.flags & kFlagLateWait) { pdl_wait_prior(); pdl_launch_dependents(); }
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -592,6 +594,8 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+    // a CTA that waited nowhere above (no item that reads v) still waits before it leaves
+    if ((p.flags & kFlagLateWait) && threadIdx.x == 0) { pdl_wait_prior(); pdl_launch_dependents(); }
 }
 
 }  // namespace
