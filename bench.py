@@ -519,7 +519,62 @@ def tensor_parallel_leg(args, wl, rank, local, world, dev):
     }
     del pools, ys, x_qkv, x_o, eng
     torch.cuda.empty_cache()
+    rec["replicated_a_scheme"] = replicated_a_leg(args, wl, rank, world, dev, n_layers)
     return rec
+
+
+def replicated_a_leg(args, wl, rank, world, dev, n_layers):
+    """The reference's own tensor-parallel layout for comparison: A replicated ``[r, h_in]``, B column-sharded
+    ``[h_out/tp, r]``, every rank reads the full x and no collective is needed
+    (lightllm/models/lora_gpu.py:25-26,33-34).  Costs tp x the A reads, saves the all-reduce and the split launches."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import ae296_b200 as L
+    from ae296_b200.pool import AdapterPool
+    from ae296_b200.workloads import SEED_BASE, torch_dtype
+    tp = world
+    dt = torch_dtype(wl.dtype)
+    T = wl.n_tokens
+    rs = int(wl.ranks.astype(np.int64).sum())
+    need = sum(rs * n_layers * (p.h_in + p.h_out // tp) * 2 for p in wl.projections)
+    free_b, _ = torch.cuda.mem_get_info()
+    fits = torch.tensor([1 if need < free_b * 0.8 else 0], device=dev)
+    dist.all_reduce(fits, op=dist.ReduceOp.MIN)
+    if int(fits.item()) == 0:
+        return {"ms_per_step": None, "note": "replicated A does not fit beside B/tp on these GPUs"}
+    g = torch.Generator(device=dev).manual_seed(SEED_BASE + wl.cfg + 100 * rank)
+    pools, ys = {}, {}
+    for p in wl.projections:
+        pool = AdapterPool.empty(wl.n_adapters, n_layers, p.h_in, p.h_out // tp, wl.ranks, wl.scalings, dtype=dt, device=dev)
+        pool.wa.normal_(0, 1.0 / float(np.sqrt(p.h_in)), generator=g)
+        pool.wb.normal_(0, 0.15, generator=g)
+        pools[p.name] = pool
+        ys[p.name] = torch.zeros(n_layers, T, p.h_out // tp, dtype=dt, device=dev)
+    h = wl.projections[0].h_in
+    x_qkv = torch.empty(n_layers, T, h, dtype=dt, device=dev).normal_(0, 1, generator=g)
+    x_o = torch.empty(n_layers, T, h, dtype=dt, device=dev).normal_(0, 1, generator=g)
+    ids = torch.from_numpy(wl.ids).to(dev)
+    batch = L.LoraBatch(T, wl.n_adapters, h, 3, dev)
+    names = [p.name for p in wl.projections]
+    stream = torch.cuda.Stream(dev)
+    tiles = wl.seq_lens is not None
+
+    def one_pass():
+        batch.set_ids(ids, pools["q"], tiles=tiles)
+        for l in range(n_layers):
+            batch.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
+            batch.apply([(x_o[l], ys["o"][l], pools["o"])], l)
+
+    ms_all = Timer(stream, world).run(capture(stream, one_pass).replay, args.steps, 3, pairs=3)
+    tms = torch.tensor([med(ms_all)], device=dev)
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    batch.workspace.check()
+    ms = float(tms.item())
+    del pools, ys, x_qkv, x_o, batch
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "collectives_per_step": 0,
+            "note": "A replicated, B column-sharded, full x on every rank (the reference's layout)"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -569,7 +624,8 @@ def main():
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"           # keeps NCCL's version banner off stdout: one JSON line only
-        dist.init_process_group("nccl", device_id=dev)
+        # a rank that fails alone must not keep the others (and the GPUs) waiting for NCCL's default ten minutes
+        dist.init_process_group("nccl", device_id=dev, timeout=__import__("datetime").timedelta(seconds=180))
 
     base = make_workload(args.workload)
     if base.cfg in (3, 4) and world > 1:
