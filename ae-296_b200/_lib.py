@@ -37,6 +37,10 @@ class Adapters(C.Structure):
                 ("packed", C.c_int32), ("scale", C.c_float), ("ranks_pow2", C.c_int32), ("total_rank", C.c_int64)]
 
 
+class TpContext(C.Structure):
+    _fields_ = [("landing", (C.c_void_p * 2) * 8), ("flags", C.c_void_p * 8), ("tp", C.c_int32), ("rank", C.c_int32)]
+
+
 class Proj(C.Structure):
     _fields_ = [("x", C.c_void_p), ("y", C.c_void_p), ("wa", C.c_void_p), ("wb", C.c_void_p),
                 ("ldx", C.c_int64), ("ldy", C.c_int64), ("h_in", C.c_int32), ("h_out", C.c_int32)]
@@ -69,6 +73,15 @@ SYMBOLS = {
                                             C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_int32, C.c_float, C.c_int32, C.c_void_p]),
     "b200_add_lora_bgmv_static_status": (C.c_int, [C.c_void_p]),
+    "b200_lora_tp_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "b200_lora_tp_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
+    "b200_lora_tp_free": (C.c_int, [C.c_void_p]),
+    "b200_lora_tp_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200_lora_tp_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b200_lora_tp_close": (C.c_int, [C.c_void_p]),
+    "b200_lora_tp_layout": (C.c_int, [C.POINTER(TpContext), C.c_int32, C.c_void_p, C.c_int32, C.c_int32]),
+    "b200_lora_tp_exchange": (C.c_int, [C.POINTER(TpContext), C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                        C.c_void_p]),
     # include/b200_cpu_assist.h
     "b200_xfer_register_pinned": (C.c_int, [C.c_void_p, C.c_size_t]),
     "b200_xfer_unregister_pinned": (C.c_int, [C.c_void_p]),

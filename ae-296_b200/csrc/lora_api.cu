@@ -349,6 +349,77 @@ int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* off
     return B200_LORA_OK;
 }
 
+// ---- tensor-parallel exchange ---------------------------------------------------------------------
+// one allocation: two landing buffers [tp][n_proj][max_tokens][64] fp32, then the arrival words
+// [2][8] and two counters, 256-byte aligned
+static size_t tp_landing_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp) {
+    return (((size_t)tp * n_proj * max_tokens * kMaxRank * 4) + 255) & ~size_t(255);
+}
+
+size_t b200_lora_tp_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp) {
+    if (max_tokens < 1 || n_proj < 1 || n_proj > kMaxProj || tp < 2 || tp > B200_LORA_TP_MAX_RANKS) return 0;
+    return 2 * tp_landing_bytes(max_tokens, n_proj, tp) + 256;
+}
+
+int b200_lora_tp_alloc(void** base, size_t bytes) {
+    if (!base || bytes == 0) return B200_LORA_ERR_NULL;
+    cudaError_t e = cudaMalloc(base, bytes);
+    if (e == cudaSuccess) e = cudaMemset(*base, 0, bytes);
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_tp_free(void* base) {
+    cudaError_t e = cudaFree(base);
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_tp_export(void* base, void* handle64) {
+    if (!base || !handle64) return B200_LORA_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, base);
+    if (e != cudaSuccess) return cuda_fail(e);
+    memcpy(handle64, &h, 64);
+    return B200_LORA_OK;
+}
+
+int b200_lora_tp_open(const void* handle64, void** mapped) {
+    if (!handle64 || !mapped) return B200_LORA_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(mapped, h, cudaIpcMemLazyEnablePeerAccess);
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_tp_close(void* mapped) {
+    cudaError_t e = cudaIpcCloseMemHandle(mapped);
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_tp_layout(b200_lora_tp* tp, int32_t r, void* base, int32_t max_tokens, int32_t n_proj) {
+    if (!tp || !base) return B200_LORA_ERR_NULL;
+    if (r < 0 || r >= B200_LORA_TP_MAX_RANKS || tp->tp < 2 || tp->tp > B200_LORA_TP_MAX_RANKS) return B200_LORA_ERR_DIM;
+    const size_t lb = tp_landing_bytes(max_tokens, n_proj, tp->tp);
+    char* b = static_cast<char*>(base);
+    tp->landing[r][0] = b;
+    tp->landing[r][1] = b + lb;
+    tp->flags[r] = b + 2 * lb;
+    return B200_LORA_OK;
+}
+
+int b200_lora_tp_exchange(const b200_lora_tp* tp, void* workspace, int32_t max_tokens, int32_t n_tokens,
+                          int32_t n_proj, int32_t skip_arrival, void* stream) {
+    if (!tp || !workspace) return B200_LORA_ERR_NULL;
+    if (tp->tp < 2 || tp->tp > B200_LORA_TP_MAX_RANKS || tp->rank < 0 || tp->rank >= tp->tp) return B200_LORA_ERR_DIM;
+    if (max_tokens < 1 || n_tokens < 1 || n_tokens > max_tokens || n_proj < 1 || n_proj > kMaxProj) return B200_LORA_ERR_DIM;
+    for (int r = 0; r < tp->tp; ++r)
+        if (!tp->landing[r][0] || !tp->landing[r][1] || !tp->flags[r]) return B200_LORA_ERR_NULL;
+    WorkspaceView w = workspace_view(workspace, max_tokens, n_proj);
+    cudaError_t e = launch_tp_exchange(tp, w.v, n_proj, max_tokens, n_tokens, &w.ctl->error, skip_arrival, sm_count(),
+                                       static_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
 int b200_lora_workspace_status(const void* workspace, void* stream) {
     if (!workspace) return B200_LORA_ERR_NULL;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -295,6 +295,8 @@ cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts
                                       int n_segs, int n_tokens, const PlanAdapters& ad, cudaStream_t s);
 cudaError_t launch_bgmv(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
 cudaError_t launch_bgmv_tma(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
+cudaError_t launch_tp_exchange(const b200_lora_tp* tp, float* v, int n_proj, int cap, int n_tokens, unsigned* err,
+                               int skip_push, int n_sm, cudaStream_t s);
 bool sgmv_tiles_supported(const ApplyParams& p);
 cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io_dtype, int n_sm, cudaStream_t s);
 

@@ -423,7 +423,7 @@ def tp_parity_check(wl, dev, rank, tp):
         ref = L.LoraBatch(T, wl.n_adapters, h_in, len(group), dev).set_ids(ids, full[0], tiles=tiles)
         y_full = [torch.zeros(T, p.h_out, dtype=torch.float32, device=dev) for p in group]
         ref.apply([(x, y, pool) for y, pool in zip(y_full, full)], 0)
-        eng = TPLora(T, wl.n_adapters, h_in // tp, len(group), tp, rank, None, dev).set_ids(ids, shard[0], tiles=tiles)
+        eng = TPLora(T, wl.n_adapters, h_in // tp, len(group), tp, rank, None, dev, exchange="peer").set_ids(ids, shard[0], tiles=tiles)
         y_sh = [torch.zeros(T, p.h_out // tp, dtype=torch.float32, device=dev) for p in group]
         eng.apply([(column_slice(x, tp, rank), y, sh) for y, sh in zip(y_sh, shard)], 0)
         torch.cuda.synchronize()
@@ -431,6 +431,7 @@ def tp_parity_check(wl, dev, rank, tp):
         for yf, ys in zip(y_full, y_sh):
             rms = float(yf.pow(2).mean().sqrt())
             worst = max(worst, float((column_slice(yf, tp, rank) - ys).abs().max()) / max(rms, 1e-30))
+        eng.close()
         del ref, eng, full, shard
     return worst
 
@@ -472,37 +473,47 @@ def tensor_parallel_leg(args, wl, rank, local, world, dev):
     x_qkv = torch.empty(n_layers, T, hi, dtype=dt, device=dev).normal_(0, 1, generator=g)
     x_o = torch.empty(n_layers, T, hi, dtype=dt, device=dev).normal_(0, 1, generator=g)
     ids = torch.from_numpy(wl.ids).to(dev)
-    eng = TPLora(T, wl.n_adapters, hi, 3, tp, rank, None, dev)
     names = [p.name for p in wl.projections]
     stream = torch.cuda.Stream(dev)
     tiles = wl.seq_lens is not None
-
-    def one_pass():
-        eng.set_ids(ids, pools["q"], tiles=tiles)
-        for l in range(n_layers):
-            eng.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
-            eng.apply([(x_o[l], ys["o"][l], pools["o"])], l)
-
-    mode = "cuda-graph"
-    with torch.cuda.stream(stream):
-        one_pass()
-        stream.synchronize()
-        dist.barrier()
-        try:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                one_pass()
-            run = graph.replay
-        except Exception:                       # NCCL inside a graph refused: time eager launches
-            mode = "eager"
-            run = one_pass
     timer = Timer(stream, world)
-    with ClockSampler(local) as clk:
-        ms_all = timer.run(run, args.steps, max(args.warmup, 3))
-    tms = torch.tensor([med(ms_all)], device=dev)
-    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-    ms = float(tms.item())
-    eng.batch.workspace.check()
+
+    def timed(exchange, sampler=None):
+        eng = TPLora(T, wl.n_adapters, hi, 3, tp, rank, None, dev, exchange=exchange)
+
+        def one_pass():
+            eng.set_ids(ids, pools["q"], tiles=tiles)
+            for l in range(n_layers):
+                eng.apply([(x_qkv[l], ys[n][l], pools[n]) for n in names if n != "o"], l)
+                eng.apply([(x_o[l], ys["o"][l], pools["o"])], l)
+
+        mode = "cuda-graph"
+        with torch.cuda.stream(stream):
+            one_pass()
+            stream.synchronize()
+            dist.barrier()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    one_pass()
+                run = graph.replay
+            except Exception:                       # a collective inside a graph refused: time eager launches
+                mode = "eager"
+                run = one_pass
+        if sampler is not None:
+            with sampler:
+                ms_all = timer.run(run, args.steps, max(args.warmup, 3))
+        else:
+            ms_all = timer.run(run, args.steps, 3, pairs=3)
+        tms = torch.tensor([med(ms_all)], device=dev)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        eng.batch.workspace.check()
+        eng.close()
+        return float(tms.item()), ms_all, mode
+
+    clk = ClockSampler(local)
+    ms, ms_all, mode = timed("peer", clk)
+    ms_nccl, _, mode_nccl = timed("nccl")
     peak, peak_src = hbm_peak()
     per_gpu = wl.bytes_per_layer(tp=tp) * n_layers + 2 * 4 * T * 64 * 4 * 2 * n_layers
     applies = n_layers * 2
@@ -510,14 +521,15 @@ def tensor_parallel_leg(args, wl, rank, local, world, dev):
         "workload": f"cfg{wl.cfg}:{wl.name}", "tp": tp, "tokens": T, "layers": n_layers, "adapters": wl.n_adapters,
         "ms_per_step": ms, "spread_ms": spread(ms_all), "tokens_per_s": T / (ms * 1e-3), "scaling": "strong",
         "dtype": "f32-accumulate/" + wl.dtype, "timing": mode,
-        "parallelism": f"tp{tp}: A row-sharded, B column-sharded, NCCL all-reduce of the fp32 [T,64] shrink partials",
+        "parallelism": f"tp{tp}: A row-sharded, B column-sharded, fp32 [T,64] shrink partials summed by the library's one-kernel exchange over peer memory",
+        "with_nccl_all_reduce": {"ms_per_step": ms_nccl, "timing": mode_nccl},
         "per_gpu_gbs": per_gpu / (ms * 1e-3) / 1e9, "frac_of_hbm": per_gpu / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
-        "tp_parity": float(parity.item()), "all_reduces_per_step": applies,
-        # per apply: shrink + fold + expand, and with prompts one tile launch per half
-        "gpu_launches_per_step": 1 + applies * (3 + (2 if tiles else 0)),
+        "tp_parity": float(parity.item()), "exchanges_per_step": applies,
+        # per apply: shrink + fold + exchange + expand, and with prompts one tile launch per half
+        "gpu_launches_per_step": 1 + applies * (4 + (2 if tiles else 0)),
         "note": note, "clocks": clk.summary(),
     }
-    del pools, ys, x_qkv, x_o, eng
+    del pools, ys, x_qkv, x_o
     torch.cuda.empty_cache()
     rec["replicated_a_scheme"] = replicated_a_leg(args, wl, rank, world, dev, n_layers)
     return rec
@@ -636,7 +648,7 @@ def main():
                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": rec["dtype"], "data": "synthetic",
                    "config": {"workload": rec["workload"], "tokens": rec["tokens"], "layers": rec["layers"],
                               "parallelism": rec["parallelism"], "l2": "inputs larger than L2", "note": rec["note"]},
-                   "roofline": {"bound": "hbm", "kernel": "whole pass per GPU (shrink + all-reduce + expand)",
+                   "roofline": {"bound": "hbm", "kernel": "whole pass per GPU (shrink + exchange + expand)",
                                 "achieved": rec["per_gpu_gbs"], "peak": hbm_peak()[0], "unit": "GB/s", "frac": rec["frac_of_hbm"],
                                 "traffic": None},
                    "tp": rec, "cpu_baseline": None, "e2e": None,

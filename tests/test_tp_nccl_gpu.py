@@ -19,7 +19,7 @@ def _free_port():
     return port
 
 
-def _rank_main(rank, world, port, q):
+def _rank_main(rank, world, port, q, exchange="nccl", fail_rank=-1):
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     sys.path[:0] = [root, os.path.join(root, "tests")]
@@ -39,8 +39,30 @@ def _rank_main(rank, world, port, q):
             assert c.x.device.index == rank
         shards = [c.pool.shard(world, rank) for c in cases]
         errs = []
+        if fail_rank >= 0:
+            # rank `fail_rank` withholds its arrival signal in the second apply: its peers' bounded wait runs
+            # out and shows as a status; nobody hangs, and the process group is torn down normally afterwards
+            import ae296_b200 as L
+            eng = TPLora(len(ids), 12, 2048 // world, 3, world, rank, None, dev, exchange="peer").set_ids(cases[0].ids_dev, shards[0])
+            ys = [torch.zeros(len(ids), c.h_out // world, dtype=torch.float32, device=dev) for c in cases]
+            xs = column_slice(cases[0].x, world, rank)
+            eng.apply([(xs, y, sh) for y, sh in zip(ys, shards)], 0)
+            torch.cuda.synchronize()
+            eng.batch.workspace.check()
+            dist.barrier()
+            eng.apply([(xs, y, sh) for y, sh in zip(ys, shards)], 0, skip_arrival=(rank == fail_rank))
+            torch.cuda.synchronize()
+            code = 0
+            try:
+                eng.batch.workspace.check()
+            except L.LoraError as e:
+                code = e.code
+            q.put((rank, code))
+            dist.barrier()
+            eng.close()
+            return
         for tiles in (False, True):
-            eng = TPLora(len(ids), 12, 2048 // world, 3, world, rank, None, dev).set_ids(cases[0].ids_dev, shards[0], tiles=tiles)
+            eng = TPLora(len(ids), 12, 2048 // world, 3, world, rank, None, dev, exchange=exchange).set_ids(cases[0].ids_dev, shards[0], tiles=tiles)
             ys = [torch.zeros(len(ids), c.h_out // world, dtype=torch.float32, device=dev) for c in cases]
             xs = column_slice(cases[0].x, world, rank)
             for _ in range(2):                 # a second apply accumulates: y = 2 * delta
@@ -51,6 +73,7 @@ def _rank_main(rank, world, port, q):
                 want = O.tp_column_slice(2 * c.oracle_delta(0), world, rank)
                 full_rms = float(np.sqrt(((2 * c.oracle_delta(0)) ** 2).mean()))
                 errs.append(float(np.abs(y.double().cpu().numpy() - want).max() / full_rms))
+            eng.close()
         q.put((rank, max(errs)))
         dist.barrier()
     finally:
@@ -71,3 +94,32 @@ def test_tplora_two_nccl_ranks_match_oracle_column_slices():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert set(res) == {0, 1} and max(res.values()) <= 2e-3, res
+
+
+def _spawn(world, **kw):
+    import torch.multiprocessing as mp
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q), kwargs=kw) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tplora_peer_exchange_matches_oracle_column_slices():
+    """The library's own exchange over peer memory instead of the NCCL all-reduce."""
+    res = _spawn(2, exchange="peer")
+    assert set(res) == {0, 1} and max(res.values()) <= 2e-3, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_that_never_arrives_is_a_timeout_status_not_a_hang():
+    res = _spawn(2, fail_rank=1)
+    assert res[0] == -11, res            # rank 0 waited for rank 1's signal and gave up
+    assert res[1] == 0, res              # rank 1 itself saw rank 0 arrive
