@@ -846,23 +846,26 @@ def main():
         gpu_ref = gpu_reference_leg(wl, dev, stream, timer, n_layers, x_qkv, x_o, pools, args.steps, cycle)
         if gpu_ref.get("value"):
             gpu_ref["ours_over_gpu_reference"] = (T / (ms * 1e-3)) / gpu_ref["value"]
+    pool_gb = round(sum(p.nbytes() for p in pools.values()) / 1e9, 3)
+    del x_qkv, x_o, pools, ys, batch
+    torch.cuda.empty_cache()
     dropin = None
     if rank == 0 and world == 1 and not args.no_dropin and not use_tiles:
-        torch.cuda.empty_cache()
-        dropin = dropin_leg(wl, dev, stream, timer, args.steps)
+        p0 = wl.projections[0]
+        need = 3 * 2 * wl.n_adapters * (wl.n_layers if wl.cfg != 0 else 32) * 16 * p0.h_in * 2 * 3.5     # its pools + the mirror's
+        if need < torch.cuda.mem_get_info()[0] * 0.8:
+            dropin = dropin_leg(wl, dev, stream, timer, args.steps)
+        else:
+            dropin = {"note": "not run: its dense pools do not fit this GPU"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu, _ = cpu_legs(wl, steps=2, warmup=1)
 
-    pool_gb = round(sum(p.nbytes() for p in pools.values()) / 1e9, 3)
     step_bytes = pass_bytes
     l2 = ("inputs larger than L2: a step touches %.0f MB of a %.2f GB pool" % (step_bytes / 1e6, pool_gb)) if step_bytes > 1.5 * L2_BYTES \
         else ("a step touches %.1f MB; consecutive steps use different layers of a %.0f MB pool (%d-step cycle), larger than L2"
               % (step_bytes / 1e6, pool_gb * 1e3, cycle))
-    del x_qkv, x_o, pools, ys
-    torch.cuda.empty_cache()
-
     tp_rec = None
     if world > 1 and base.cfg == 1 and not args.no_tp:
         tp_rec = {}

@@ -37,6 +37,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 APP = os.path.join(HERE, "_ref", "app.py")
 SEGMENTS = ["shm_array", "shm_out_q", "shm_out_k", "shm_out_v", "shm_out_o"]
 ROWS_MAX = 200                 # rows one projection's doorbell range can name (app.py:111-128)
+ROW_TOKENS_MAX = 200           # tokens of one row (the worker sees the count through one byte)
 BASES = {"q": 2, "k": 202, "v": 402, "o": 2}
 
 
@@ -175,7 +176,11 @@ def time_reference_workers(wl, layers: int = 0, steps: int = 2, warmup: int = 1,
         rows = [(1, int(a)) for a in wl.ids[:nd]]
         pos = nd
         for ln in wl.seq_lens:
-            rows.append((int(ln), int(wl.ids[pos])))
+            # the worker reads the row's token count as ONE byte of the shared word (app.py:99,130), and
+            # the reference caps prompts at 256 tokens (lightllm/models/lora_cpu.py:14): a longer prompt is
+            # served as several rows of at most ROW_TOKENS_MAX tokens
+            for c0 in range(0, int(ln), ROW_TOKENS_MAX):
+                rows.append((min(ROW_TOKENS_MAX, int(ln) - c0), int(wl.ids[pos])))
             pos += int(ln)
     else:
         rows = [(1, int(a)) for a in wl.ids]
