@@ -1,6 +1,7 @@
 // extern "C" entry points declared in include/b200_lora.h: argument checks and launches only.
 #include <string.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "lora_common.cuh"
@@ -52,15 +53,23 @@ EncodeTiledFn encode_tiled() {
 bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner,
                    uint32_t box_rows, CUtensorMapSwizzle swizzle, uint64_t pitch = 0) {
     if (pitch == 0) pitch = inner;
-    struct Entry { const void* base; uint64_t inner, rows, pitch; uint32_t bi, br; int sw; CUtensorMap map; };
-    static Entry cache[256];
-    static int n_cached = 0, next = 0;
+    // Encoded maps are kept in a hashed, 4-way set-associative table (4096 entries): an eager loop over
+    // many layers presents a few hundred (base pointer, shape) keys per step, and a look-up touches one set.
+    struct Entry { const void* base; uint64_t inner, rows, pitch; uint32_t bi, br; int sw; bool used; CUtensorMap map; };
+    constexpr int kSets = 1024, kWays = 4;
+    static Entry cache[kSets][kWays];
+    static unsigned char victim[kSets];
     static std::mutex mu;
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h = (h ^ (inner * 0x9E3779B97F4A7C15ull) ^ (rows * 0xC2B2AE3D27D4EB4Full) ^ (pitch << 21) ^ ((uint64_t)box_inner << 40) ^
+         ((uint64_t)box_rows << 48) ^ ((uint64_t)swizzle << 56)) * 0xFF51AFD7ED558CCDull;
+    const int set_idx = (int)((h >> 40) % kSets);
+    Entry* set = cache[set_idx];
     std::lock_guard<std::mutex> lock(mu);
-    for (int i = 0; i < n_cached; ++i) {
-        const Entry& e = cache[i];
-        if (e.base == base && e.inner == inner && e.rows == rows && e.pitch == pitch && e.bi == box_inner && e.br == box_rows &&
-            e.sw == (int)swizzle) { *out = e.map; return true; }
+    for (int i = 0; i < kWays; ++i) {
+        const Entry& e = set[i];
+        if (e.used && e.base == base && e.inner == inner && e.rows == rows && e.pitch == pitch && e.bi == box_inner &&
+            e.br == box_rows && e.sw == (int)swizzle) { *out = e.map; return true; }
     }
     EncodeTiledFn fn = encode_tiled();
     if (!fn) return false;
@@ -73,12 +82,51 @@ bool tensor_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t 
            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
-    Entry& e = cache[next];
-    e.base = base; e.inner = inner; e.rows = rows; e.pitch = pitch; e.bi = box_inner; e.br = box_rows; e.sw = (int)swizzle; e.map = m;
-    next = (next + 1) % 256;
-    if (n_cached < 256) ++n_cached;
+    int way = -1;
+    for (int i = 0; i < kWays && way < 0; ++i)
+        if (!set[i].used) way = i;
+    if (way < 0) {                                          // a full set: its ways are replaced in turn
+        way = victim[set_idx];
+        victim[set_idx] = (unsigned char)((way + 1) % kWays);
+    }
+    Entry& e = set[way];
+    e.base = base; e.inner = inner; e.rows = rows; e.pitch = pitch; e.bi = box_inner; e.br = box_rows; e.sw = (int)swizzle;
+    e.used = true; e.map = m;
     *out = m;
     return true;
+}
+
+// The tile kernels (tall runs) and the BGMV kernels (everything else) of one apply touch disjoint
+// rows of y, v and the split-K partials, so they run as two chains: the tiles on a side stream
+// that forks from the caller's stream and joins it again before the call returns.  Each chain is
+// a string of short dependent launches whose start-up and tail leave SMs idle; the other chain's
+// CTAs fill them.  One side stream per host thread and device, created on first use (outside
+// stream capture: a first use inside a capture runs the two chains one after the other).
+struct SideStream {
+    cudaStream_t stream;
+    cudaEvent_t fork, join;
+    int state;                // 0 not tried, 1 ready, -1 unavailable
+};
+SideStream* side_stream(cudaStream_t caller) {
+    static const bool serial = [] { const char* v = getenv("B200_LORA_SERIAL_TILES"); return v && v[0] == '1'; }();
+    if (serial) return nullptr;
+    thread_local SideStream side[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SideStream& ss = side[dev];
+    if (ss.state == 0) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(caller, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            return nullptr;                                  // try again on a later call
+        }
+        const bool ok = cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) cudaGetLastError();
+        ss.state = ok ? 1 : -1;
+    }
+    return ss.state == 1 ? &ss : nullptr;
 }
 
 // rows of an A pool viewed as a [rows, h_in] matrix
@@ -295,6 +343,7 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n_sm = sm_count();
     cudaError_t e = cudaSuccess;
+    SideStream* side = nullptr;
     if (!sgmv_tiles_supported(p)) p.flags |= B200_LORA_NO_TENSOR;
     if (!(p.flags & B200_LORA_NO_TENSOR)) {
         SgmvParams sp;
@@ -319,7 +368,15 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
             }
         }
         if (!ok) p.flags |= B200_LORA_NO_TENSOR;        // no driver entry point: everything on the BGMV kernels
-        else e = launch_sgmv_tiles(p, sp, io_dtype, n_sm, s);
+        else {
+            side = side_stream(s);
+            if (side && (cudaEventRecord(side->fork, s) != cudaSuccess ||
+                         cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)) {
+                cudaGetLastError();
+                side = nullptr;
+            }
+            e = launch_sgmv_tiles(p, sp, io_dtype, n_sm, side ? side->stream : s);
+        }
     }
     bool fast = fast_ranks(adapters);
     for (int i = 0; i < n_proj; ++i)
@@ -336,6 +393,11 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
             }
     }
     if (e == cudaSuccess) e = fast ? launch_bgmv_tma(p, io_dtype, n_sm, s) : launch_bgmv(p, io_dtype, n_sm, s);
+    if (side) {                                             // the side stream always joins, also after a failed launch
+        cudaError_t j = cudaEventRecord(side->join, side->stream);
+        if (j == cudaSuccess) j = cudaStreamWaitEvent(s, side->join, 0);
+        if (e == cudaSuccess) e = j;
+    }
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }
 

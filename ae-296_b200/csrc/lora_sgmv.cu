@@ -58,7 +58,11 @@ constexpr int kD1Col = 0, kD2Col = 128;     // two D1 buffers of 64 columns, two
 constexpr unsigned kSpinLimit = 1u << 22;
 // Launcher-internal flag (above the public bits): the two launches of a batch with few tiles.  The
 // phase-1 launch cuts every (tile, projection) pair along k, one CTA per part; the parts' fp32 sums
-// go to the split-K partial buffers and the last CTA to finish a pair adds them, in part order, into v.
+// go to the split-K partial buffers and nothing else happens there: a small kernel between the two
+// launches adds a pair's parts, in part order, into v (all SMs, coalesced, every part's load in
+// flight at once; having the CTA that finishes a pair last add them kept a few SMs busy for longer
+// than the whole of phase 1, and having every phase-2 CTA add them itself reads them once per
+// column part).
 constexpr int kFlagKSplit = 1 << 16;
 constexpr int kMaxKSplit = 8;
 // Launcher-internal: the phase-2 launch that follows it.  It is launched with programmatic stream
@@ -181,6 +185,51 @@ __device__ __forceinline__ TileInfo tile_info(const SgmvParams& sp, const ApplyP
     return t;
 }
 
+// k parts per (tile, projection) pair of a phase-1 launch with few pairs: as many as there are CTAs
+// per pair, bounded by the k blocks of the narrowest input and by the partial buffers of the workspace
+__device__ __forceinline__ int ksplit_of(const ApplyParams& p, int n_cta, int base_items) {
+    if (base_items <= 0) return 1;
+    int ksplit = max(1, min(kMaxKSplit, n_cta / base_items));
+    int h_min = p.proj[0].h_in, h_max = p.proj[0].h_in;
+    for (int i = 1; i < p.n_proj; ++i) { h_min = min(h_min, p.proj[i].h_in); h_max = max(h_max, p.proj[i].h_in); }
+    return max(1, min(ksplit, min(h_min / kBK, max_kchunks(h_max))));
+}
+
+// Adds the k parts of every (tile, projection) pair into v after a k-split phase-1 launch of
+// `n_cta` CTAs.  One unit = 16 rows of a pair = 256 threads, a thread per four rank columns.
+__global__ void __launch_bounds__(256) sgmv_ksum_kernel(const __grid_constant__ ApplyParams p, int n_cta) {
+    pdl_wait_prior();
+    if (threadIdx.x == 0) pdl_launch_dependents();
+    PlanView pv = plan_view(p.plan, p.cap, p.n_adapters);
+    WorkspaceView ws = workspace_view(p.workspace, p.cap, p.n_proj);
+    const PlanHeader hdr = *pv.hdr;
+    if (!plan_usable(hdr, p, &ws.ctl->error)) return;
+    const int base_items = hdr.n_tiles * p.n_proj;
+    const int ksplit = ksplit_of(p, n_cta, base_items);
+    if (ksplit <= 1) return;                               // phase 1 wrote v itself
+    const size_t kstride = (size_t)p.n_proj * p.cap * kMaxRank;
+    const int r16 = threadIdx.x >> 4, f = threadIdx.x & 15;
+    for (int u = blockIdx.x; u < base_items * (kBM / 16); u += gridDim.x) {
+        const int pair = u >> 3, tile = pair / p.n_proj, proj = pair - tile * p.n_proj;
+        const int pos0 = pv.tile_tab[2 * tile], e1 = pv.tile_tab[2 * tile + 1];
+        const int rank = pv.seg_rank[e1 >> 8], valid = (e1 & 255) + 1;
+        const int row = (u & 7) * 16 + r16;
+        if (row >= valid || f * 4 >= rank) continue;
+        const size_t vidx = ((size_t)proj * p.cap + pos0 + row) * kMaxRank + f * 4;
+        float4 g[kMaxKSplit];
+#pragma unroll
+        for (int kp = 0; kp < kMaxKSplit; ++kp) {
+            g[kp] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (kp < ksplit) g[kp] = __ldcg(reinterpret_cast<const float4*>(ws.partial + kp * kstride + vidx));
+        }
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int kp = 0; kp < kMaxKSplit; ++kp)
+            if (kp < ksplit) { a.x += g[kp].x; a.y += g[kp].y; a.z += g[kp].z; a.w += g[kp].w; }
+        *reinterpret_cast<float4*>(ws.v + vidx) = a;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kSgmvThreads, 1)
 sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ SgmvParams sp) {
@@ -201,7 +250,6 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + kSmemTiles);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + kNumBars);
     int* ystate = reinterpret_cast<int*>(tmem_slot + 1);        // per y slot: projection (< 0: no store), column, row
-    int* last_flag = ystate + 3 * kYSMax;                       // k-split phase 1: this CTA adds the pair's parts
     // barrier indices
     const int FULL1 = 0, EMPTY1 = kS1, FULL2 = 2 * kS1, EMPTY2 = 2 * kS1 + kS2;
     const int D1_FULL = 2 * kS1 + 2 * kS2, D1_EMPTY = D1_FULL + 2, V_READY = D1_FULL + 4, V_FREE = D1_FULL + 5;
@@ -225,15 +273,10 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const int base_items = n_tiles * p.n_proj;
     const int n_cta = (int)gridDim.x;
     const int n_full = (base_items / n_cta) * n_cta, n_rem = base_items - n_full;
-    // k parts per pair of a phase-1 launch with few pairs (both launches compute the same number)
-    // (bounded by the k blocks of the narrowest input and by the partial buffers the workspace holds)
-    int ksplit = ((p.flags & kFlagKSplit) && base_items > 0) ? max(1, min(kMaxKSplit, n_cta / base_items)) : 1;
-    {
-        int h_min = p.proj[0].h_in, h_max = p.proj[0].h_in;
-        for (int i = 1; i < p.n_proj; ++i) { h_min = min(h_min, p.proj[i].h_in); h_max = max(h_max, p.proj[i].h_in); }
-        ksplit = max(1, min(ksplit, min(h_min / kBK, max_kchunks(h_max))));
-    }
+    const int ksplit = (p.flags & kFlagKSplit) ? ksplit_of(p, n_cta, base_items) : 1;
     const bool k_items = ksplit > 1 && (p.flags & B200_LORA_ONLY_SHRINK);
+    // a launch of phase 2 only: both column halves of the epilogue build V (each its half of the rank columns)
+    const bool both = !do1;
     int nsplit = 1;
     if (n_rem > 0 && !(p.flags & B200_LORA_ONLY_SHRINK)) nsplit = min(8, max(1, (2 * n_cta) / n_rem));
     for (int i = 0; i < p.n_proj; ++i)                    // every part must own at least one column slice
@@ -254,7 +297,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
         for (int s = 0; s < kS1; ++s) { mbar_init(bar(FULL1 + s), 1); mbar_init(bar(EMPTY1 + s), 1); }
         for (int s = 0; s < kS2; ++s) { mbar_init(bar(FULL2 + s), 1); mbar_init(bar(EMPTY2 + s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(D1_FULL + b), 1); mbar_init(bar(D1_EMPTY + b), 128); }
-        mbar_init(bar(V_READY), 128);
+        mbar_init(bar(V_READY), do1 ? 128 : 256);
         mbar_init(bar(V_FREE), 1);
         for (int b = 0; b < 2; ++b) { mbar_init(bar(D2_FULL + b), 1); mbar_init(bar(D2_EMPTY + b), kEpiWarps * 32); }
         for (int b = 0; b < kYSMax; ++b) { mbar_init(bar(Y_FULL + b), 1); mbar_init(bar(Y_DONE + b), kEpiWarps * 32); }
@@ -437,7 +480,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
             const ProjArgs& pj = p.proj[proj];
             if (half != 0 && !do2) continue;
             // ---- D1 -> V (16-bit hi / lo), swizzled K-major rows of rank*2 bytes: first warp of the quadrant
-            if (half == 0) {
+            if (half == 0 || both) {
             float d1[64];
             // fp32 row of the intermediate: the reduced v, or this k part's slot when phase 1 is cut along k
             const size_t vidx = ((size_t)proj * p.cap + t.pos0 + row) * kMaxRank;
@@ -465,47 +508,15 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                             if (c * 4 < t.rank)
                                 reinterpret_cast<float4*>(vrow)[c] = make_float4(d1[4 * c], d1[4 * c + 1], d1[4 * c + 2], d1[4 * c + 3]);
                     }
-                    if (k_items) {
-                        // The CTA that finishes a pair's last k part adds the parts, in part order
-                        // whoever it is, into v.  Nobody waits: arrivals are counted per pair.
-                        __threadfence();
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (tid == 128) {
-                            const unsigned seen = atomicAdd(&ws.counters[rest], 1u);
-                            const bool last = seen == (unsigned)(ksplit - 1);
-                            if (last) ws.counters[rest] = 0u;             // zero at rest
-                            *last_flag = last ? 1 : 0;
-                        }
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (*reinterpret_cast<volatile int*>(last_flag) != 0) {
-                            __threadfence();
-                            if (row < t.valid) {
-#pragma unroll
-                                for (int i = 0; i < 64; ++i) d1[i] = 0.f;
-                                for (int kp = 0; kp < ksplit; ++kp) {
-                                    const float4* src = reinterpret_cast<const float4*>(ws.partial + kp * kstride + vidx);
-#pragma unroll
-                                    for (int c = 0; c < 16; ++c)
-                                        if (c * 4 < t.rank) {
-                                            const float4 g = __ldcg(src + c);
-                                            d1[4 * c] += g.x; d1[4 * c + 1] += g.y; d1[4 * c + 2] += g.z; d1[4 * c + 3] += g.w;
-                                        }
-                                }
-#pragma unroll
-                                for (int c = 0; c < 16; ++c)
-                                    if (c * 4 < t.rank)
-                                        reinterpret_cast<float4*>(ws.v + vidx)[c] = make_float4(d1[4 * c], d1[4 * c + 1], d1[4 * c + 2], d1[4 * c + 3]);
-                            }
-                        }
-                    }
                     continue;
                 }
-            } else {                                         // expand half only: v was summed by the caller
+            } else {
+                // expand half only: v was summed by the caller (or by the kernel that adds the k parts)
                 if (p.flags & kFlagLateWait) { pdl_wait_prior(); pdl_launch_dependents(); }
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (c * 4 < t.rank && row < t.valid) f = reinterpret_cast<const float4*>(vrow)[c];
+                    if ((c >> 3) == half && c * 4 < t.rank && row < t.valid) f = __ldcg(reinterpret_cast<const float4*>(vrow) + c);
                     d1[4 * c] = f.x; d1[4 * c + 1] = f.y; d1[4 * c + 2] = f.z; d1[4 * c + 3] = f.w;
                 }
             }
@@ -517,7 +528,7 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
                 unsigned char* rl = vlo + (row >> 3) * (8 * rb) + (row & 7) * rb;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    if (c * 8 < t.rank) {
+                    if (c * 8 < t.rank && (!both || (c >> 2) == half)) {
                         uint4 h, l;
                         unsigned* hp = reinterpret_cast<unsigned*>(&h);
                         unsigned* lp = reinterpret_cast<unsigned*>(&l);
@@ -634,6 +645,8 @@ cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io
     if (halves_given) return launch(q);
     q.flags = p.flags | B200_LORA_ONLY_SHRINK | kFlagKSplit;
     cudaError_t e = launch(q);
+    if (e != cudaSuccess) return e;
+    e = launch_pdl(sgmv_ksum_kernel, dim3(n_sm), dim3(256), 0, s, q, n_sm);
     if (e != cudaSuccess) return e;
     q.flags = p.flags | B200_LORA_ONLY_EXPAND | kFlagLateWait;
     if (io_dtype == B200_LORA_F16)
