@@ -38,7 +38,8 @@ class Adapters(C.Structure):
 
 
 class TpContext(C.Structure):
-    _fields_ = [("landing", (C.c_void_p * 2) * 8), ("flags", C.c_void_p * 8), ("tp", C.c_int32), ("rank", C.c_int32)]
+    _fields_ = [("landing", (C.c_void_p * 2) * 8), ("flags", C.c_void_p * 8), ("tp", C.c_int32), ("rank", C.c_int32),
+                ("set_stride", C.c_size_t)]
 
 
 class Proj(C.Structure):
@@ -82,6 +83,9 @@ SYMBOLS = {
     "b200_lora_tp_layout": (C.c_int, [C.POINTER(TpContext), C.c_int32, C.c_void_p, C.c_int32, C.c_int32]),
     "b200_lora_tp_exchange": (C.c_int, [C.POINTER(TpContext), C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                         C.c_void_p]),
+    "b200_lora_apply_tp": (C.c_int, [C.POINTER(Proj), C.c_int32, C.POINTER(Adapters), C.c_void_p, C.c_int32,
+                                     C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                     C.c_size_t, C.POINTER(TpContext), C.c_int32, C.c_void_p]),
     # include/b200_cpu_assist.h
     "b200_xfer_register_pinned": (C.c_int, [C.c_void_p, C.c_size_t]),
     "b200_xfer_unregister_pinned": (C.c_int, [C.c_void_p]),

@@ -292,10 +292,23 @@ int b200_lora_workspace_init(void* workspace, size_t bytes, void* stream) {
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }
 
-int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
-                    const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
-                    int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes_, void* stream) {
+static bool tp_usable(const b200_lora_tp* tp) {
+    if (tp->tp < 2 || tp->tp > B200_LORA_TP_MAX_RANKS || tp->rank < 0 || tp->rank >= tp->tp || tp->set_stride == 0) return false;
+    for (int r = 0; r < tp->tp; ++r)
+        if (!tp->landing[r][0] || !tp->landing[r][1] || !tp->flags[r]) return false;
+    return true;
+}
+
+// One apply.  With `tp` it is the tensor-parallel form: each chain (the tiles on the side stream,
+// the BGMV kernels on the caller's) runs its shrink half, the exchange of its own rows of v over
+// the ranks, and its expand half.
+static int apply_core(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
+                      const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
+                      int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes_, void* stream,
+                      const b200_lora_tp* tp, int skip_arrival) {
     if (!projs || !plan || !workspace) return B200_LORA_ERR_NULL;
+    if (tp && !tp_usable(tp)) return B200_LORA_ERR_DIM;
+    if (tp && (flags & (B200_LORA_ONLY_SHRINK | B200_LORA_ONLY_EXPAND))) return B200_LORA_ERR_DIM;
     int rc = check_adapters(adapters);
     if (rc) return rc;
     if (n_proj < 1 || n_proj > kMaxProj || max_tokens < 1 || n_tokens < 1 || n_tokens > max_tokens) return B200_LORA_ERR_DIM;
@@ -375,7 +388,16 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
                 cudaGetLastError();
                 side = nullptr;
             }
-            e = launch_sgmv_tiles(p, sp, io_dtype, n_sm, side ? side->stream : s);
+            cudaStream_t ts = side ? side->stream : s;
+            if (!tp) e = launch_sgmv_tiles(p, sp, io_dtype, n_sm, ts);
+            else {
+                ApplyParams h = p;
+                h.flags = p.flags | B200_LORA_ONLY_SHRINK;
+                e = launch_sgmv_tiles(h, sp, io_dtype, n_sm, ts);
+                if (e == cudaSuccess) e = launch_tp_exchange_rows(tp, 1, true, false, p, 0, io_dtype, skip_arrival, n_sm, ts);
+                h.flags = p.flags | B200_LORA_ONLY_EXPAND;
+                if (e == cudaSuccess) e = launch_sgmv_tiles(h, sp, io_dtype, n_sm, ts);
+            }
         }
     }
     bool fast = fast_ranks(adapters);
@@ -392,13 +414,41 @@ int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora
                                      CU_TENSOR_MAP_SWIZZLE_NONE);
             }
     }
-    if (e == cudaSuccess) e = fast ? launch_bgmv_tma(p, io_dtype, n_sm, s) : launch_bgmv(p, io_dtype, n_sm, s);
+    auto bgmv = [&](const ApplyParams& q) { return fast ? launch_bgmv_tma(q, io_dtype, n_sm, s) : launch_bgmv(q, io_dtype, n_sm, s); };
+    if (e == cudaSuccess && !tp) e = bgmv(p);
+    if (e == cudaSuccess && tp) {
+        // the TMA shrink kernel leaves its split-K slots and the exchange adds them up; the general one leaves v
+        ApplyParams h = p;
+        h.flags = p.flags | B200_LORA_ONLY_SHRINK | (fast ? B200_LORA_KEEP_PARTIALS : 0);
+        e = bgmv(h);
+        if (e == cudaSuccess)
+            e = launch_tp_exchange_rows(tp, 0, false, (p.flags & B200_LORA_NO_TENSOR) != 0, p, fast ? bgmv_tma_shrink_grid(n_sm) : 0,
+                                        io_dtype, skip_arrival, n_sm, s);
+        h.flags = p.flags | B200_LORA_ONLY_EXPAND;
+        if (e == cudaSuccess) e = bgmv(h);
+    }
     if (side) {                                             // the side stream always joins, also after a failed launch
         cudaError_t j = cudaEventRecord(side->join, side->stream);
         if (j == cudaSuccess) j = cudaStreamWaitEvent(s, side->join, 0);
         if (e == cudaSuccess) e = j;
     }
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
+}
+
+int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
+                    const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
+                    int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes_, void* stream) {
+    return apply_core(projs, n_proj, adapters, plan, max_tokens, n_tokens, layer, io_dtype, y_dtype, flags, workspace,
+                      workspace_bytes_, stream, nullptr, 0);
+}
+
+int b200_lora_apply_tp(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
+                       const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
+                       int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes_, const b200_lora_tp* tp,
+                       int32_t skip_arrival, void* stream) {
+    if (!tp) return B200_LORA_ERR_NULL;
+    return apply_core(projs, n_proj, adapters, plan, max_tokens, n_tokens, layer, io_dtype, y_dtype, flags, workspace,
+                      workspace_bytes_, stream, tp, skip_arrival);
 }
 
 int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* offset_bytes, size_t* size_bytes) {
@@ -412,15 +462,15 @@ int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* off
 }
 
 // ---- tensor-parallel exchange ---------------------------------------------------------------------
-// one allocation: two landing buffers [tp][n_proj][max_tokens][64] fp32, then the arrival words
-// [2][8] and two counters, 256-byte aligned
+// one allocation: two sets of two landing buffers [tp][n_proj][max_tokens][64] of 8-byte packets (value,
+// exchange number), then per set the exchange counter and the CTA counter; everything 256-byte aligned
 static size_t tp_landing_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp) {
-    return (((size_t)tp * n_proj * max_tokens * kMaxRank * 4) + 255) & ~size_t(255);
+    return (((size_t)tp * n_proj * max_tokens * kMaxRank * 8) + 255) & ~size_t(255);
 }
 
 size_t b200_lora_tp_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp) {
     if (max_tokens < 1 || n_proj < 1 || n_proj > kMaxProj || tp < 2 || tp > B200_LORA_TP_MAX_RANKS) return 0;
-    return 2 * tp_landing_bytes(max_tokens, n_proj, tp) + 256;
+    return 4 * tp_landing_bytes(max_tokens, n_proj, tp) + B200_LORA_TP_COUNTER_BYTES;
 }
 
 int b200_lora_tp_alloc(void** base, size_t bytes) {
@@ -465,7 +515,8 @@ int b200_lora_tp_layout(b200_lora_tp* tp, int32_t r, void* base, int32_t max_tok
     char* b = static_cast<char*>(base);
     tp->landing[r][0] = b;
     tp->landing[r][1] = b + lb;
-    tp->flags[r] = b + 2 * lb;
+    tp->flags[r] = b + 4 * lb;
+    tp->set_stride = 2 * lb;
     return B200_LORA_OK;
 }
 
@@ -474,10 +525,8 @@ int b200_lora_tp_exchange(const b200_lora_tp* tp, void* workspace, int32_t max_t
     if (!tp || !workspace) return B200_LORA_ERR_NULL;
     if (tp->tp < 2 || tp->tp > B200_LORA_TP_MAX_RANKS || tp->rank < 0 || tp->rank >= tp->tp) return B200_LORA_ERR_DIM;
     if (max_tokens < 1 || n_tokens < 1 || n_tokens > max_tokens || n_proj < 1 || n_proj > kMaxProj) return B200_LORA_ERR_DIM;
-    for (int r = 0; r < tp->tp; ++r)
-        if (!tp->landing[r][0] || !tp->landing[r][1] || !tp->flags[r]) return B200_LORA_ERR_NULL;
-    WorkspaceView w = workspace_view(workspace, max_tokens, n_proj);
-    cudaError_t e = launch_tp_exchange(tp, w.v, n_proj, max_tokens, n_tokens, &w.ctl->error, skip_arrival, sm_count(),
+    if (!tp_usable(tp)) return B200_LORA_ERR_NULL;
+    cudaError_t e = launch_tp_exchange(tp, workspace, n_proj, max_tokens, n_tokens, skip_arrival, sm_count(),
                                        static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? B200_LORA_OK : cuda_fail(e);
 }

@@ -40,6 +40,7 @@
 // Semantics: add_lora_bgmv(y, x, wa_T_all, wb_T_all, indicies, layer_idx, scale) of the
 // reference (lightllm/models/lora_gpu.py:138,150,162), pools as at :33-40.
 #include "lora_common.cuh"
+#include "lora_fold.cuh"
 
 namespace b200lora {
 
@@ -371,67 +372,6 @@ __device__ __forceinline__ void shrink_flush(const ApplyParams& p, const Workspa
         float s = 0.f;
         for (int w = 0; w < ksplit; ++w) s += red[(w * 8 + tok) * rp + i];
         dst[tok * kMaxRank + i] = s;
-    }
-}
-
-// The split-K slots of one (projection, work segment): the runs of the shrink kernel start at
-// the segment's first unit and wherever a CTA's item range starts inside the segment, and a
-// run's slot is the index, inside the segment, of its first unit.  `seg_first` is the list
-// index of the segment's first unit, `per_cta` the length of a CTA's range, `n_chunks` the
-// units of the segment that lie inside the matrix (they come first).
-struct SlotWalk {
-    int j, step, n_chunks;
-    __device__ __forceinline__ SlotWalk(int seg_first, int per_cta, int n_chunks_) : j(0), n_chunks(n_chunks_) {
-        step = per_cta - seg_first % per_cta;              // distance to the next range start
-    }
-    __device__ __forceinline__ bool valid() const { return j < n_chunks; }
-    __device__ __forceinline__ void next(int per_cta) { j += step; step = per_cta; }
-};
-// list index of the first shrink unit of the segment that starts at plan unit `u0`
-__device__ __forceinline__ int shrink_seg_first(const ApplyParams& p, int n_units, int proj, int u0) {
-    int base = 0;
-#pragma unroll
-    for (int i = 0; i < kMaxProj - 1; ++i)
-        if (i < proj) base += n_units * p.proj[i].n_super_in;
-    return base + u0 * p.proj[proj].n_super_in;
-}
-__device__ __forceinline__ int shrink_chunks(const ApplyParams& p, int proj, int rank) {
-    const int wshift = rank <= 16 ? 9 : rank == 32 ? 8 : 7;
-    return (p.proj[proj].h_in + (1 << wshift) - 1) >> wshift;
-}
-
-// Adds up the slots of one segment, ascending, for NQ quads (four consecutive rank indices of
-// one token each) at once: the loads of all quads and of up to NS slots are in flight together.
-template <typename T, int NQ, int NS = 4>
-__device__ __forceinline__ void fold_quads(const ApplyParams& p, const WorkspaceView& ws, const size_t (&off)[NQ],
-                                           const bool (&on)[NQ], int seg_first, int per_cta, int n_chunks, float4 (&s)[NQ]) {
-    const size_t cstride = (size_t)p.n_proj * p.cap * kMaxRank;
-#pragma unroll
-    for (int i = 0; i < NQ; ++i) s[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    SlotWalk sw(seg_first, per_cta, n_chunks);
-    while (sw.valid()) {
-        float4 v[NS][NQ];
-#pragma unroll
-        for (int q = 0; q < NS; ++q) {
-            const bool live = sw.valid();
-#pragma unroll
-            for (int i = 0; i < NQ; ++i) {
-                v[q][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (live && on[i]) v[q][i] = __ldcg(reinterpret_cast<const float4*>(ws.partial + (size_t)sw.j * cstride + off[i]));
-            }
-            if (live) sw.next(per_cta);
-        }
-#pragma unroll
-        for (int q = 0; q < NS; ++q)
-#pragma unroll
-            for (int i = 0; i < NQ; ++i) { s[i].x += v[q][i].x; s[i].y += v[q][i].y; s[i].z += v[q][i].z; s[i].w += v[q][i].w; }
-    }
-    if (p.flags & B200_LORA_MID_ROUND) {
-#pragma unroll
-        for (int i = 0; i < NQ; ++i) {
-            s[i].x = Cvt<T>::round1(s[i].x); s[i].y = Cvt<T>::round1(s[i].y);
-            s[i].z = Cvt<T>::round1(s[i].z); s[i].w = Cvt<T>::round1(s[i].w);
-        }
     }
 }
 
@@ -948,22 +888,35 @@ __global__ void __launch_bounds__(128) fold_partials_kernel(const __grid_constan
     const int n_units = (p.flags & B200_LORA_NO_TENSOR) ? hdr.n_units : hdr.n_units_short;
     const int per_cta = (n_units * p.total_super_in + shrink_grid - 1) / shrink_grid;
     const int proj = blockIdx.y;
-    // the units with sub-range 0 are the first units of the work segments
-    for (int u0 = blockIdx.x; u0 < n_units; u0 += gridDim.x) {
-        const UnitRec* rec = reinterpret_cast<const UnitRec*>(pv.unit_tab) + u0;
-        if (rec->sub != 0) continue;
-        const int r = rec->rank, ntok = rec->ntok, start = rec->start;
-        const int seg_first = shrink_seg_first(p, n_units, proj, u0);
-        const int n_chunks = shrink_chunks(p, proj, r);
-        const int qshift = 31 - __clz(r >> 2);
-        for (int idx = threadIdx.x; idx < ((ntok * r) >> 2); idx += blockDim.x) {
-            const int t = idx >> qshift, k4 = (idx & ((r >> 2) - 1)) * 4;
-            const size_t off = ((size_t)proj * p.cap + start + t) * kMaxRank + k4;
-            const size_t offs[1] = {off};
-            const bool on[1] = {true};
-            float4 sum[1];
-            fold_quads<T, 1>(p, ws, offs, on, seg_first, per_cta, n_chunks, sum);
-            *reinterpret_cast<float4*>(ws.v + off) = sum[0];
+    // The units with sub-range 0 are the first units of the work segments.  A warp looks at 32 records at
+    // once (one load round) and then works through the heads among them.
+    const int lane = threadIdx.x & 31, warp_g = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int n_warps = gridDim.x * (blockDim.x >> 5);
+    for (int base = warp_g * 32; base < n_units; base += n_warps * 32) {
+        const int u = base + lane;
+        int r = 0, ntok = 0, start = 0;
+        if (u < n_units) {
+            const UnitRec* rec = reinterpret_cast<const UnitRec*>(pv.unit_tab) + u;
+            if (rec->sub == 0) { r = rec->rank; ntok = rec->ntok; start = rec->start; }
+        }
+        unsigned heads = __ballot_sync(0xffffffffu, ntok > 0);
+        while (heads) {
+            const int src = __ffs(heads) - 1;
+            heads &= heads - 1;
+            const int hr = __shfl_sync(0xffffffffu, r, src), hn = __shfl_sync(0xffffffffu, ntok, src);
+            const int hs = __shfl_sync(0xffffffffu, start, src);
+            const int seg_first = shrink_seg_first(p, n_units, proj, base + src);
+            const int n_chunks = shrink_chunks(p, proj, hr);
+            const int qshift = 31 - __clz(hr >> 2);
+            for (int idx = lane; idx < ((hn * hr) >> 2); idx += 32) {
+                const int t = idx >> qshift, k4 = (idx & ((hr >> 2) - 1)) * 4;
+                const size_t off = ((size_t)proj * p.cap + hs + t) * kMaxRank + k4;
+                const size_t offs[1] = {off};
+                const bool on[1] = {true};
+                float4 sum[1];
+                fold_quads<T, 1>(p, ws, offs, on, seg_first, per_cta, n_chunks, sum);
+                *reinterpret_cast<float4*>(ws.v + off) = sum[0];
+            }
         }
     }
 }
@@ -1001,6 +954,8 @@ cudaError_t launch_pair(const ApplyParams& p, int n_sm, cudaStream_t s) {
 }
 
 }  // namespace
+
+int bgmv_tma_shrink_grid(int n_sm) { return n_sm * kCtasPerSm; }
 
 cudaError_t launch_bgmv_tma(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s) {
     if (io_dtype == B200_LORA_F16) return launch_pair<__half>(p, n_sm, s);

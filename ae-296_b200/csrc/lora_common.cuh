@@ -295,8 +295,13 @@ cudaError_t launch_plan_from_segments(void* plan, int cap, const int* seg_starts
                                       int n_segs, int n_tokens, const PlanAdapters& ad, cudaStream_t s);
 cudaError_t launch_bgmv(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
 cudaError_t launch_bgmv_tma(const ApplyParams& p, int io_dtype, int n_sm, cudaStream_t s);
-cudaError_t launch_tp_exchange(const b200_lora_tp* tp, float* v, int n_proj, int cap, int n_tokens, unsigned* err,
-                               int skip_push, int n_sm, cudaStream_t s);
+int bgmv_tma_shrink_grid(int n_sm);       // CTAs of the TMA shrink kernel (whoever adds up its split-K slots needs it)
+cudaError_t launch_tp_exchange(const b200_lora_tp* tp, void* workspace, int n_proj, int cap, int n_tokens, int skip_push,
+                               int n_sm, cudaStream_t s);
+// one exchange of a tensor-parallel apply: the rows of the plan's tiles (`tall`) or of its BGMV work segments
+// (`fold_grid` > 0: the BGMV rows' v is still the split-K slots of a TMA shrink kernel of that many CTAs)
+cudaError_t launch_tp_exchange_rows(const b200_lora_tp* tp, int set, bool tall, bool all_units, const ApplyParams& p, int fold_grid,
+                                    int io_dtype, int skip_push, int n_sm, cudaStream_t s);
 bool sgmv_tiles_supported(const ApplyParams& p);
 cudaError_t launch_sgmv_tiles(const ApplyParams& p, const SgmvParams& sp, int io_dtype, int n_sm, cudaStream_t s);
 

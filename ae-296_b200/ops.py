@@ -135,10 +135,13 @@ class LoraWorkspace:
 
 
 def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan: LoraPlan, layer: int,
-          workspace: LoraWorkspace, flags: int = 0, adapters: Optional[Adapters] = None) -> None:
+          workspace: LoraWorkspace, flags: int = 0, adapters: Optional[Adapters] = None, tp_ctx=None,
+          skip_arrival: bool = False) -> None:
     """``y += scale_a * (x @ A_a^T) @ B_a^T`` for up to four projections ``(x, y, pool)`` of one layer.
 
-    All pools must share one adapter table (ranks, scalings, layout)."""
+    All pools must share one adapter table (ranks, scalings, layout).  With ``tp_ctx`` (the library's
+    peer-exchange context of a tensor-parallel rank) the call is ``b200_lora_apply_tp``: ``x``, ``y`` and the
+    pools are this rank's shards and the shrink result is summed over the ranks inside the call."""
     if not 1 <= len(projs) <= _lib.MAX_PROJ:
         raise ValueError("1..4 projections per call")
     arr = (Proj * len(projs))()
@@ -163,6 +166,12 @@ def apply(projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], plan:
         arr[i] = Proj(x.data_ptr(), y.data_ptr(), pool.wa.data_ptr(), pool.wb.data_ptr(),
                       x.stride(0), y.stride(0), pool.h_in, pool.h_out)
     ad = adapters if adapters is not None else adapters_of(projs[0][2])
+    if tp_ctx is not None:
+        check(_lib.lib().b200_lora_apply_tp(
+            arr, len(projs), C.byref(ad), plan.buf.data_ptr(), plan.max_tokens, int(projs[0][0].shape[0]), int(layer),
+            _DT[io], _DT[ydt], int(flags), workspace.buf.data_ptr(), workspace.nbytes, C.byref(tp_ctx),
+            1 if skip_arrival else 0, _stream(projs[0][0].device)), "apply_tp")
+        return
     check(_lib.lib().b200_lora_apply(
         arr, len(projs), C.byref(ad), plan.buf.data_ptr(), plan.max_tokens, int(projs[0][0].shape[0]), int(layer),
         _DT[io], _DT[ydt],
@@ -339,10 +348,10 @@ class LoraBatch:
         self.tiles = tiles
         return self
 
-    def apply(self, projs, layer: int, flags: int = 0) -> None:
+    def apply(self, projs, layer: int, flags: int = 0, tp_ctx=None, skip_arrival: bool = False) -> None:
         if not self.tiles:
             flags |= _lib.NO_TENSOR
-        apply(projs, self.plan, layer, self.workspace, flags)
+        apply(projs, self.plan, layer, self.workspace, flags, tp_ctx=tp_ctx, skip_arrival=skip_arrival)
 
 
 def add_lora_bgmv_v2(y, x, pool: AdapterPool, indicies, layer_idx: int, flags: int = 0) -> None:

@@ -7,6 +7,9 @@ The only exchange is the sum of the small fp32 shrink partials ``[T, 64]`` per p
 
     shrink (ONLY_SHRINK)  ->  all_reduce(v, SUM) over NCCL/NVLink  ->  expand (ONLY_EXPAND)
 
+or, with ``exchange="peer"``, one library call per apply (``b200_lora_apply_tp``) that sums the partials with
+the library's own kernels over peer memory.
+
 The reference instead replicates A and needs no collective (lightllm/models/lora_gpu.py:25-26,33-34)
 at the price of reading A ``tp`` times; that scheme is ``LoraBatch.apply`` with the full ``x``.
 One process per GPU; ``torch.distributed`` supplies the process group.
@@ -120,11 +123,15 @@ class TPLora:
         host, with which tests check that the peers give up instead of hanging."""
         n = len(projs)
         t = projs[0][0].shape[0]
-        self.batch.apply(projs, layer, _lib.ONLY_SHRINK)
         if self.peer is not None:
-            self.peer.exchange(self.batch.workspace, t, n, skip_arrival)
-        else:
-            allreduce_partials(self._v[:n, :t] if t == self._v.shape[1] else self._v[:n], self.group)
+            # one library call: both halves and, between them, the exchange of the rows each kernel chain
+            # owns (tall runs on the tile kernels' side stream, the rest beside the BGMV kernels)
+            if n > self.peer.n_proj:
+                raise ValueError("more projections than the exchange buffers were sized for")
+            self.batch.apply(projs, layer, 0, tp_ctx=self.peer.ctx, skip_arrival=skip_arrival)
+            return
+        self.batch.apply(projs, layer, _lib.ONLY_SHRINK)
+        allreduce_partials(self._v[:n, :t] if t == self._v.shape[1] else self._v[:n], self.group)
         self.batch.apply(projs, layer, _lib.ONLY_EXPAND)
 
     def close(self) -> None:

@@ -156,20 +156,22 @@ int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* off
 /* ---- tensor-parallel exchange over peer memory (no counterpart in the reference, which replicates A) -----
  * Sums the fp32 shrink result v over the tensor-parallel ranks between a B200_LORA_ONLY_SHRINK and a
  * B200_LORA_ONLY_EXPAND apply with ONE kernel per rank: every rank stores its partial into a landing
- * buffer in every peer's memory (plain stores over NVLink), raises an arrival word there, waits - with
- * a bound - for its peers' arrival words and adds the landing slots up in rank order (all ranks obtain
- * the same bits).  Takes the place of an NCCL all-reduce of b200_lora_workspace_v_region.
+ * buffer in every peer's memory (plain 8-byte stores over NVLink, each carrying a value and the number of
+ * the exchange), polls - with a bound - its own landing buffer until its peers' packets show that number
+ * and adds the values up in rank order (all ranks obtain the same bits).  No flag, fence or barrier stands
+ * between data and consumer.  Takes the place of an NCCL all-reduce of b200_lora_workspace_v_region.
  *
  * Set-up, once per process: b200_lora_tp_alloc a buffer of b200_lora_tp_bytes, b200_lora_tp_export its
  * 64-byte handle, hand the handles round (any host channel), b200_lora_tp_open every peer's handle and
  * fill b200_lora_tp with b200_lora_tp_layout.  Every rank must issue the same sequence of exchanges.
  * A rank whose peer never arrives gives up after a second or two: the exchange leaves v incomplete and
  * b200_lora_workspace_status returns B200_LORA_ERR_TIMEOUT; nothing hangs. */
-enum { B200_LORA_TP_MAX_RANKS = 8 };
+enum { B200_LORA_TP_MAX_RANKS = 8, B200_LORA_TP_COUNTER_BYTES = 24576 };
 typedef struct b200_lora_tp {
     void* landing[B200_LORA_TP_MAX_RANKS][2];  /* [r][b]: landing buffer b of rank r as mapped into this process */
-    void* flags[B200_LORA_TP_MAX_RANKS];       /* [r]: rank r's arrival words (and, for r == rank, the local counters) */
+    void* flags[B200_LORA_TP_MAX_RANKS];       /* [r]: rank r's counter block (only that of r == rank is used) */
     int32_t tp, rank;
+    size_t set_stride;                         /* bytes from the landing buffers of set 0 to those of set 1 */
 } b200_lora_tp;
 size_t b200_lora_tp_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp);
 int b200_lora_tp_alloc(void** base, size_t bytes);                 /* cudaMalloc + zero fill (IPC-exportable) */
@@ -179,10 +181,20 @@ int b200_lora_tp_open(const void* handle64, void** mapped);       /* cudaIpcOpen
 int b200_lora_tp_close(void* mapped);
 /* Fills tp->landing[r] / tp->flags[r] from rank r's buffer base (own base for r == rank, mapped bases else). */
 int b200_lora_tp_layout(b200_lora_tp* tp, int32_t r, void* base, int32_t max_tokens, int32_t n_proj);
-/* The exchange on `workspace`'s v region.  skip_arrival != 0 withholds this rank's arrival words (a failure
+/* The exchange on `workspace`'s v region.  skip_arrival != 0 withholds this rank's packets (a failure
  * made on the host, for tests of the peers' bounded wait). */
 int b200_lora_tp_exchange(const b200_lora_tp* tp, void* workspace, int32_t max_tokens, int32_t n_tokens,
                           int32_t n_proj, int32_t skip_arrival, void* stream);
+/* b200_lora_apply for a tensor-parallel rank in ONE call: shrink half, exchange, expand half.  `flags` as
+ * for b200_lora_apply, without the ONLY_* bits.  Two exchanges run per apply, each with its own landing
+ * buffers and arrival words: that of the rows of tall runs between the two tile launches (on a side stream
+ * inside the call), that of all other rows between the BGMV halves; each moves only the rank columns of its
+ * rows, and each hides behind the other chain's kernels.  With B200_LORA_NO_TENSOR there is one exchange.
+ * All ranks must make the same calls with the same flags on the same plan contents. */
+int b200_lora_apply_tp(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
+                       const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
+                       int32_t y_dtype, int32_t flags, void* workspace, size_t workspace_bytes,
+                       const b200_lora_tp* tp, int32_t skip_arrival, void* stream);
 
 /* Reads the workspace's sticky device-side error word (synchronises `stream`):
  * B200_LORA_OK, B200_LORA_ERR_TIMEOUT if a bounded wait inside a kernel expired, or
