@@ -92,9 +92,12 @@ struct RowSel {
 template <typename F>
 __device__ __forceinline__ void tp_for_rows(const PlanView& pv, const RowSel& rs, F&& f) {
     const int lane = threadIdx.x & 31;
-    // the warps are dealt over the projections first: warp w works on projection w % n_proj
+    // The work of a thread is a chain of dependent memory round trips, so the exchange is as quick as that
+    // chain is short: the warps are dealt over the projections and over the quarters of a group first (a
+    // group of 8 rows of rank 64 is 128 float4s: one per lane of four warps).
     const int warp_all = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), warps_all = gridDim.x * (blockDim.x >> 5);
-    const int pj = warp_all % rs.n_proj, warp_g = warp_all / rs.n_proj, n_warps = warps_all / rs.n_proj;
+    const int ways = rs.n_proj * 4, sub = warp_all % ways;
+    const int pj = sub >> 2, quarter = sub & 3, warp_g = warp_all / ways, n_warps = warps_all / ways;
     if (warp_g >= n_warps) return;
     // Unit records: a warp looks at 32 at once (one load round for all of them) and works through the few
     // that head a work segment.  Rows and tiles: every candidate is a group, one per warp and round.
@@ -129,7 +132,7 @@ __device__ __forceinline__ void tp_for_rows(const PlanView& pv, const RowSel& rs
             const int g_pos = __shfl_sync(0xffffffffu, pos, src), g_rows = __shfl_sync(0xffffffffu, rows, src);
             const int q = (__shfl_sync(0xffffffffu, rank, src) + 3) >> 2, n = g_rows * q;
             const int g_unit = base + src, g_rank = __shfl_sync(0xffffffffu, rank, src);
-            for (int idx = lane; idx < n; idx += 32) {
+            for (int idx = quarter * 32 + lane; idx < n; idx += 128) {
                 const int r = idx / q;
                 f(((size_t)pj * rs.cap + g_pos + r) * (kMaxRank / 4) + (idx - r * q), pj, g_unit, g_rank);
             }
@@ -206,12 +209,22 @@ __global__ void __launch_bounds__(256) tp_exchange_kernel(const TpArgs a, const 
     bool gave_up = false;
     tp_for_rows(pv, rs, [&](size_t idx, int, int, int) {
         const float4 own = v4[idx];
+        const uint4* mine = a.peer_landing[a.rank][buf] + idx * 2;
+        uint4 pk[kTpMaxRanks][2];                                         // every peer's packets requested before any is looked at
+#pragma unroll
+        for (int s = 0; s < kTpMaxRanks; ++s)
+            if (s < a.tp && s != a.rank) {
+                pk[s][0] = ld_packets(mine + (size_t)s * slot_f4 * 2);
+                pk[s][1] = ld_packets(mine + (size_t)s * slot_f4 * 2 + 1);
+            }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < a.tp; ++s) {                                  // rank order: the same sum on every rank
+#pragma unroll
+        for (int s = 0; s < kTpMaxRanks; ++s) {                           // rank order: the same sum on every rank
+            if (s >= a.tp) continue;
             float4 x = own;
             if (s != a.rank) {
-                const uint4* src = a.peer_landing[a.rank][buf] + ((size_t)s * slot_f4 + idx) * 2;
-                uint4 p0 = ld_packets(src), p1 = ld_packets(src + 1);
+                const uint4* src = mine + (size_t)s * slot_f4 * 2;
+                uint4 p0 = pk[s][0], p1 = pk[s][1];
                 for (unsigned i = 0; !gave_up && (p0.y != epoch || p0.w != epoch || p1.y != epoch || p1.w != epoch); ++i) {
                     if (i >= kTpSpinLimit || ((i & 0xffu) == 0xffu && *reinterpret_cast<volatile unsigned*>(err) != 0u)) {
                         gave_up = true;                                   // this thread stops waiting for anything
@@ -242,7 +255,7 @@ __global__ void __launch_bounds__(256) tp_exchange_kernel(const TpArgs a, const 
 int exchange_grid(int n_tokens, int n_proj, int n_sm) {
     // a warp per (group of <= 8 rows, projection) where the batch allows it: the work of a thread is a
     // chain of dependent memory round trips, so the exchange is as quick as that chain is short
-    long long grid = ((long long)(n_tokens + 7) / 8 * n_proj + 7) / 8;
+    long long grid = ((long long)(n_tokens + 7) / 8 * n_proj * 4 + 7) / 8;
     if (grid > n_sm) grid = n_sm;
     if (grid > kTpHintCtas) grid = kTpHintCtas;
     return grid < 8 ? 8 : (int)grid;
