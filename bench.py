@@ -437,8 +437,9 @@ def tp_parity_check(wl, dev, rank, tp):
 
 
 def tensor_parallel_leg(args, wl, rank, local, world, dev):
-    """Workloads 3 and 4 on N GPUs: A sharded along hidden, B along output, NCCL all-reduce of the fp32
-    shrink partials between the two halves.  Total work is fixed: strong scaling.  Returns the record."""
+    """Workloads 3 and 4 on N GPUs: A sharded along hidden, B along output, the fp32 shrink partials summed
+    over the ranks between the two halves (the library's exchange over peer memory; the NCCL all-reduce is
+    timed beside it).  Total work is fixed: strong scaling.  Returns the record."""
     import numpy as np
     import torch
     import torch.distributed as dist
@@ -521,12 +522,13 @@ def tensor_parallel_leg(args, wl, rank, local, world, dev):
         "workload": f"cfg{wl.cfg}:{wl.name}", "tp": tp, "tokens": T, "layers": n_layers, "adapters": wl.n_adapters,
         "ms_per_step": ms, "spread_ms": spread(ms_all), "tokens_per_s": T / (ms * 1e-3), "scaling": "strong",
         "dtype": "f32-accumulate/" + wl.dtype, "timing": mode,
-        "parallelism": f"tp{tp}: A row-sharded, B column-sharded, fp32 [T,64] shrink partials summed by the library's one-kernel exchange over peer memory",
+        "parallelism": f"tp{tp}: A row-sharded, B column-sharded, one library call per apply; the fp32 shrink partials (rank columns of the rows present) are summed by the library's exchange kernels over peer memory",
         "with_nccl_all_reduce": {"ms_per_step": ms_nccl, "timing": mode_nccl},
         "per_gpu_gbs": per_gpu / (ms * 1e-3) / 1e9, "frac_of_hbm": per_gpu / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_src,
         "tp_parity": float(parity.item()), "exchanges_per_step": applies,
-        # per apply: shrink + fold + exchange + expand, and with prompts one tile launch per half
-        "gpu_launches_per_step": 1 + applies * (4 + (2 if tiles else 0)),
+        # per apply: shrink, exchange (adds up the split-K slots itself), expand; with prompts the tile kernels'
+        # chain beside it: shrink half, exchange, expand half
+        "gpu_launches_per_step": 1 + applies * (3 + (3 if tiles else 0)),
         "note": note, "clocks": clk.summary(),
     }
     del pools, ys, x_qkv, x_o
@@ -698,8 +700,9 @@ def main():
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
 
     def tile_launches(n_proj):
-        # one launch, or two when the batch can hold fewer (tile, projection) pairs than the GPU has SMs
-        return 0 if not use_tiles else (2 if (T // 128 + 1) * n_proj < n_sm else 1)
+        # one launch, or three (shrink half cut along k, the kernel that adds the parts, expand half) when the
+        # batch can hold fewer (tile, projection) pairs than the GPU has SMs
+        return 0 if not use_tiles else (3 if (T // 128 + 1) * n_proj < n_sm else 1)
 
     launches_per_step = 1 + layers_per_step * (4 + tile_launches(3) + tile_launches(1))
 
