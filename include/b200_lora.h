@@ -141,7 +141,13 @@ int b200_lora_workspace_init(void* workspace, size_t workspace_bytes, void* stre
  * io_dtype: type of x, wa, wb (F16 | BF16).  y_dtype: io_dtype or F32.  n_tokens: rows of x
  * and y (the value the plan was built with).  Unless B200_LORA_NO_TENSOR is set, tall
  * contiguous segments of rank 16/32/64 run on the tcgen05 tile kernel, the rest on the BGMV
- * kernels; decode-only batches should set the flag and save that kernel's launch. */
+ * kernels; decode-only batches should set the flag and save that kernel's launch.  The two
+ * kinds touch disjoint rows, and the tile launches run on a side stream inside the call (forked
+ * from `stream` and joined to it again before the call returns, so the call stays ordered on
+ * `stream` and captures into a CUDA graph as a fork and a join).  The side stream is created by
+ * the first such call of a host thread on a device, which should be made outside stream capture
+ * (inside one it runs the launches one after the other); B200_LORA_SERIAL_TILES=1 in the
+ * environment keeps everything on `stream`. */
 int b200_lora_apply(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
                     const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer,
                     int32_t io_dtype, int32_t y_dtype, int32_t flags, void* workspace,
