@@ -194,3 +194,35 @@ def test_more_pairs_than_sms_single_launch():
         assert torch.equal(b, a.to(torch.float16))
     for a, b in zip(run(torch.float16), y16):
         assert torch.equal(a, b)
+
+
+def test_mixed_apply_in_a_cuda_graph_forks_and_joins():
+    """An apply with tall runs and other rows runs its tile launches on a side stream inside the call; captured
+    into a CUDA graph that is a fork and a join.  Replays must accumulate the oracle's delta once each, bit for
+    bit the same as the eager call, and work that follows on the caller's stream must see the tiles' rows."""
+    rng = np.random.default_rng(31)
+    n = 10
+    ranks = rng.choice([16, 32, 64], n).astype(np.int32)
+    ids = np.concatenate([rng.integers(0, n, 90), np.repeat([7, 2], [200, 130])]).astype(np.int32)
+    c = Case(len(ids), n, 1024, 768, ranks, "bf16", seed=29, ids=ids)
+    batch = L.LoraBatch(c.T, n, 1024, 1).set_ids(c.ids_dev, c.pool, tiles=True)
+    y_eager = torch.zeros(c.T, c.h_out, dtype=torch.float32, device="cuda")
+    batch.apply([(c.x, y_eager, c.pool)], 0)              # also the first call on this device: made outside capture
+    torch.cuda.synchronize()
+    y = torch.zeros_like(y_eager)
+    total = torch.zeros(1, dtype=torch.float64, device="cuda")
+    s = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            batch.apply([(c.x, y, c.pool)], 0)
+            total.copy_(y.double().sum().reshape(1))       # ordered after the join: sees tall and short rows
+    y.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    batch.workspace.check()
+    assert torch.equal(y, y_eager)
+    assert abs(float(total) - float(y_eager.double().sum())) <= 1e-6 * float(y_eager.double().abs().sum())
+    g.replay()
+    torch.cuda.synchronize()
+    assert rel_err(y.double().cpu().numpy(), 2 * c.oracle_delta(0)) <= TOL

@@ -74,6 +74,23 @@ def _rank_main(rank, world, port, q, exchange="nccl", fail_rank=-1):
                 full_rms = float(np.sqrt(((2 * c.oracle_delta(0)) ** 2).mean()))
                 errs.append(float(np.abs(y.double().cpu().numpy() - want).max() / full_rms))
             eng.close()
+        if exchange == "peer":
+            # the exchange as a call of its own between the two halves (b200_lora_tp_exchange: every row, all 64 columns)
+            from ae296_b200 import _lib
+            eng = TPLora(len(ids), 12, 2048 // world, 3, world, rank, None, dev, exchange="peer").set_ids(cases[0].ids_dev, shards[0])
+            ys = [torch.zeros(len(ids), c.h_out // world, dtype=torch.float32, device=dev) for c in cases]
+            xs = column_slice(cases[0].x, world, rank)
+            projs = [(xs, y, sh) for y, sh in zip(ys, shards)]
+            eng.batch.apply(projs, 0, _lib.ONLY_SHRINK)
+            eng.peer.exchange(eng.batch.workspace, len(ids), len(projs))
+            eng.batch.apply(projs, 0, _lib.ONLY_EXPAND)
+            torch.cuda.synchronize()
+            eng.batch.workspace.check()
+            for c, y in zip(cases, ys):
+                want = O.tp_column_slice(c.oracle_delta(0), world, rank)
+                full_rms = float(np.sqrt((c.oracle_delta(0) ** 2).mean()))
+                errs.append(float(np.abs(y.double().cpu().numpy() - want).max() / full_rms))
+            eng.close()
         q.put((rank, max(errs)))
         dist.barrier()
     finally:
