@@ -277,10 +277,29 @@ sgmv_tile_kernel(const __grid_constant__ ApplyParams p, const __grid_constant__ 
     const bool k_items = ksplit > 1 && (p.flags & B200_LORA_ONLY_SHRINK);
     // a launch of phase 2 only: both column halves of the epilogue build V (each its half of the rank columns)
     const bool both = !do1;
+    // Column parts of the pairs of the last round.  A launch of both phases cuts them in about 2 * n_cta parts
+    // (every part redoes phase 1, and measured against fewer parts the finer cut still wins).  A launch of
+    // phase 2 only has nothing to redo: the CTAs work through ceil(n_rem * parts / n_cta) parts each and a part
+    // costs a fixed start (reading v, building V) plus 1/parts of the pair's copies.
     int nsplit = 1;
-    if (n_rem > 0 && !(p.flags & B200_LORA_ONLY_SHRINK)) nsplit = min(8, max(1, (2 * n_cta) / n_rem));
-    for (int i = 0; i < p.n_proj; ++i)                    // every part must own at least one column slice
-        nsplit = min(nsplit, (p.proj[i].h_out + kBN - 1) / kBN);
+    if (n_rem > 0 && !(p.flags & B200_LORA_ONLY_SHRINK)) {
+        int max_parts = 8;
+        float c2 = 0.f;                                    // KB of B and y boxes per pair, at the largest rank
+        for (int i = 0; i < p.n_proj; ++i) {              // every part must own at least one column slice
+            max_parts = min(max_parts, (p.proj[i].h_out + kBN - 1) / kBN);
+            c2 += (float)(2 * kBM + 64) * p.proj[i].h_out * 2.f / 1024.f;
+        }
+        c2 /= p.n_proj;
+        if (do1) nsplit = min(max_parts, max(1, (2 * n_cta) / n_rem));
+        else {
+            float best = 3.0e38f;
+            for (int ns = 1; ns <= max_parts; ++ns) {
+                const int rounds = (n_rem * ns + n_cta - 1) / n_cta;
+                const float cost = rounds * (96.f + c2 / ns);
+                if (cost < best * 0.98f) { best = cost; nsplit = ns; }   // more parts only where they clearly pay
+            }
+        }
+    }
     const int n_items = k_items ? base_items * ksplit : n_full + n_rem * nsplit;
     // item -> pair, part, parts of the pair (parts of k in a k-split phase-1 launch, else of the output columns)
     auto decode = [&](int item, int& rest, int& part, int& parts) {
