@@ -769,27 +769,42 @@ def main():
     e2e = None
     if not args.no_e2e:
         # One host->device copy per layer (its two activations sit side by side in one buffer) and one
-        # device->host copy per group of layers (a layer's four outputs are column ranges of its
+        # device->host copy per group of layers (eight groups per pass) (a layer's four outputs are column ranges of its
         # [T, sum(h_out)] block; the kernels take the row pitch).
         h_in0 = wl.projections[0].h_in
         widths = [p.h_out for p in wl.projections]
         offs = [sum(widths[:i]) for i in range(len(widths))]
         nl = layers_per_step
-        dx = torch.empty(nl, 2, T, h_in0, dtype=dt, device=dev)
-        dx[:, 0].copy_(x_qkv[:nl]); dx[:, 1].copy_(x_o[:nl])
-        hx = torch.empty(dx.shape, dtype=dt).pin_memory().copy_(dx.cpu())
-        y_all = torch.zeros(nl, T, sum(widths), dtype=dt, device=dev)
-        yv = {n: y_all[:, :, o:o + w] for n, o, w in zip(names, offs, widths)}
-        hy = torch.empty(y_all.shape, dtype=dt).pin_memory()
+        # Two sets of device buffers alternate from step to step, as a serving loop would have them: a step's
+        # uploads wait only for the compute of the step before last (which read the same x buffers), its
+        # compute only for the download of the step before last (which read the same y buffers), so the
+        # downloads, the slowest part, run back to back.
+        dxs = [torch.empty(nl, 2, T, h_in0, dtype=dt, device=dev) for _ in range(2)]
+        for d in dxs:
+            d[:, 0].copy_(x_qkv[:nl]); d[:, 1].copy_(x_o[:nl])
+        hx = torch.empty(dxs[0].shape, dtype=dt).pin_memory().copy_(dxs[0].cpu())
+        y_alls = [torch.zeros(nl, T, sum(widths), dtype=dt, device=dev) for _ in range(2)]
+        yvs = [{n: ya[:, :, o:o + w] for n, o, w in zip(names, offs, widths)} for ya in y_alls]
+        hy = torch.empty(y_alls[0].shape, dtype=dt).pin_memory()
         copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        group = max(1, nl // 4)
+        group = max(1, nl // 8)
+        x_free = [None, None]          # recorded on `stream` when a step's compute is done with its x buffers
+        y_free = [None, None]          # recorded on `copy_out` when a step's downloads are done with its y buffers
+        step_no = [0]
 
         def e2e_step():
+            b = step_no[0] & 1
+            step_no[0] += 1
+            dx, y_all, yv = dxs[b], y_alls[b], yvs[b]
             with torch.cuda.stream(stream):
                 ids.copy_(ids_host, non_blocking=True)
                 batch.set_ids(ids, pools["q"], tiles=use_tiles)
+                if y_free[b] is not None:
+                    stream.wait_event(y_free[b])
             ev_in, ev_done = [], {}
             with torch.cuda.stream(copy_in):
+                if x_free[b] is not None:
+                    copy_in.wait_event(x_free[b])
                 for l in range(nl):
                     dx[l].copy_(hx[l], non_blocking=True)
                     ev = torch.cuda.Event(); ev.record(copy_in); ev_in.append(ev)
@@ -800,13 +815,14 @@ def main():
                     batch.apply([(dx[l, 1], yv["o"][l], pools["o"])], l)
                     if (l + 1) % group == 0 or l == nl - 1:
                         ev = torch.cuda.Event(); ev.record(stream); ev_done[l] = ev
+                x_free[b] = torch.cuda.Event(); x_free[b].record(stream)
             with torch.cuda.stream(copy_out):
                 lo = 0
                 for l in sorted(ev_done):
                     copy_out.wait_event(ev_done[l])
                     hy[lo:l + 1].copy_(y_all[lo:l + 1], non_blocking=True)
                     lo = l + 1
-            stream.wait_stream(copy_out)
+                y_free[b] = torch.cuda.Event(); y_free[b].record(copy_out)
 
         for _ in range(2):
             e2e_step()
@@ -819,6 +835,7 @@ def main():
         e0.record(stream)
         for _ in range(k):
             e2e_step()
+        stream.wait_stream(copy_out)                      # the last step's result has reached the host
         e1.record(stream)
         torch.cuda.synchronize()
         wall = (time.perf_counter() - t0) / k * 1e3
@@ -839,10 +856,10 @@ def main():
         d2h = hy.numel() * 2
         e2e = {"value": total_tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e,
-               "h2d_alone_gbs": copy_rate(lambda: dx.copy_(hx, non_blocking=True), h2d),
-               "d2h_alone_gbs": copy_rate(lambda: hy.copy_(y_all, non_blocking=True), d2h),
-               "d2h_copies_per_step": -(-nl // group), "numa": numa}
-        del dx, hx, y_all, hy
+               "h2d_alone_gbs": copy_rate(lambda: dxs[0].copy_(hx, non_blocking=True), h2d),
+               "d2h_alone_gbs": copy_rate(lambda: hy.copy_(y_alls[0], non_blocking=True), d2h),
+               "d2h_copies_per_step": -(-nl // group), "device_buffer_sets": 2, "numa": numa}
+        del dxs, hx, y_alls, yvs, hy
 
     gpu_ref = None
     if rank == 0 and world == 1 and not args.no_gpu_reference:
