@@ -9,14 +9,18 @@ the scheduler simulator (scheduler/scheduler/manager.py:52-98).
 Two policies:
 
 * ``"mod"``       adapter ``a`` lives on GPU ``a % G`` (stateless, what a router can compute alone);
-* ``"balanced"``  adapters are dealt to GPUs by decreasing token count, each to the GPU with the
-                  fewest tokens so far (longest-processing-time-first), so that a skewed
-                  popularity (a few hot adapters) does not overload one GPU.
+* ``"balanced"``  adapters are dealt to GPUs by decreasing load, each to the GPU with the least
+                  load so far (longest-processing-time-first), so that a skewed popularity (a few
+                  hot adapters) does not overload one GPU.  The load of an adapter is its token
+                  count, or, when the adapters' ranks are given, an estimate of the bytes its
+                  tokens make the kernels move: the delta path is bound by memory traffic, an
+                  adapter's weights are read once per work segment of eight tokens, and a rank-64
+                  adapter costs eight times a rank-8 one.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 
@@ -42,12 +46,30 @@ class Placement:
         return out
 
 
+WORK_SEGMENT_TOKENS = 8      # the kernels read an adapter's weights once per this many of its tokens
+TOKEN_COST_IN_RANK_ROWS = 1.5  # bytes of one token's x and y (read, read + write) relative to one rank row of A and B
+
+
+def adapter_load(counts: np.ndarray, ranks: Optional[Sequence[int]] = None) -> np.ndarray:
+    """Per-adapter load of a batch with ``counts[a]`` tokens of adapter ``a``: the token count, or with
+    ``ranks`` an estimate of the memory traffic in units of one rank row of A and B."""
+    counts = np.asarray(counts, np.int64)
+    if ranks is None:
+        return counts.astype(np.float64)
+    r = np.asarray(ranks, np.float64)
+    if r.shape != counts.shape:
+        raise ValueError("one rank per adapter")
+    segments = -(-counts // WORK_SEGMENT_TOKENS)
+    return segments * r + TOKEN_COST_IN_RANK_ROWS * counts
+
+
 def place_by_adapter(ids: Sequence[int], n_gpus: int, n_adapters: int, policy: str = "balanced",
-                     resident_all: bool = True) -> Placement:
+                     resident_all: bool = True, ranks: Optional[Sequence[int]] = None) -> Placement:
     """Splits a batch with per-token adapter ``ids`` over ``n_gpus`` GPUs.
 
     ``resident_all=True`` places every one of the ``n_adapters`` adapters (a serving pool holds
     adapters that the current batch does not use); otherwise only the batch's adapters.
+    ``ranks`` (one per adapter) makes the ``"balanced"`` policy balance estimated bytes instead of tokens.
     """
     ids = np.asarray(ids, np.int64)
     if n_gpus < 1:
@@ -61,16 +83,17 @@ def place_by_adapter(ids: Sequence[int], n_gpus: int, n_adapters: int, policy: s
         if not resident_all:
             gpu_of[counts == 0] = -1
     elif policy == "balanced":
-        load = np.zeros(n_gpus, np.int64)
+        cost = adapter_load(counts, ranks)
+        load = np.zeros(n_gpus, np.float64)
         held = np.zeros(n_gpus, np.int64)
-        order = np.argsort(-counts, kind="stable")           # hottest first; ties by adapter id
+        order = np.argsort(-cost, kind="stable")             # heaviest first; ties by adapter id
         for a in order:
             if counts[a] == 0 and not resident_all:
                 continue
-            # fewest tokens first, then fewest adapters, then lowest GPU index: deterministic
+            # least load first, then fewest adapters, then lowest GPU index: deterministic
             g = int(np.lexsort((np.arange(n_gpus), held, load))[0])
             gpu_of[a] = g
-            load[g] += counts[a]
+            load[g] += cost[a]
             held[g] += 1
     else:
         raise ValueError(f"unknown policy {policy!r}")

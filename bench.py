@@ -607,11 +607,11 @@ def placed_workload(base, world, rank):
     n_g, t_g = base.n_adapters * world, base.n_tokens * world
     ranks = rng.choice(np.unique(base.ranks), n_g).astype(np.int32)
     ids = rng.choice(n_g, t_g, p=zipf_probs(n_g, 1.0)).astype(np.int32)
-    pl = place_by_adapter(ids, world, n_g, "balanced")
+    pl = place_by_adapter(ids, world, n_g, "balanced", ranks=ranks)      # balances estimated bytes, not tokens
     mine = pl.adapters[rank]
     wl = dataclasses.replace(base, n_adapters=len(mine), ranks=ranks[mine], ids=pl.local_ids[rank].copy(),
                              n_decode=len(pl.tokens[rank]))
-    info = {"policy": "balanced", "global_tokens": t_g, "global_adapters": n_g,
+    info = {"policy": "balanced by estimated bytes (rank-weighted work segments)", "global_tokens": t_g, "global_adapters": n_g,
             "tokens_per_gpu": [int(len(t)) for t in pl.tokens], "adapters_per_gpu": [int(len(a)) for a in pl.adapters]}
     return wl, info, t_g
 

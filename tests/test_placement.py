@@ -71,3 +71,28 @@ def test_sub_batches_reassemble_to_the_unsplit_delta():
     assert np.allclose(pl.scatter(parts, H, np.float64), full, rtol=0, atol=1e-12)
     with pytest.raises(ValueError):
         place_by_adapter([0, 12], 2, 12)
+
+
+def test_balanced_by_bytes_evens_out_ragged_ranks():
+    """With ranks given the policy balances what the kernels move: an adapter's weights once per work
+    segment of eight tokens, a rank-64 adapter eight times a rank-8 one."""
+    from ae296_b200.placement import adapter_load
+    rng = np.random.default_rng(5)
+    n, t, g = 512, 2048, 8
+    ranks = rng.choice([8, 16, 32, 64], n).astype(np.int32)
+    p = 1.0 / np.arange(1, n + 1)
+    ids = rng.choice(n, t, p=p / p.sum()).astype(np.int32)
+    cost = adapter_load(np.bincount(ids, minlength=n), ranks)
+    spread = {}
+    for name, kw in (("tokens", {}), ("bytes", {"ranks": ranks})):
+        pl = place_by_adapter(ids, g, n, "balanced", **kw)
+        loads = np.array([cost[a].sum() for a in pl.adapters])
+        spread[name] = loads.max() / loads.mean()
+        assert sorted(np.concatenate(pl.tokens).tolist()) == list(range(t))          # every token placed once
+        again = place_by_adapter(ids, g, n, "balanced", **kw)
+        assert np.array_equal(pl.gpu_of_adapter, again.gpu_of_adapter)               # deterministic
+    assert spread["bytes"] <= 1.02 and spread["bytes"] < spread["tokens"]
+    # an adapter with 9 tokens is two work segments; unused adapters cost nothing
+    assert adapter_load(np.array([9, 0, 1]), [64, 64, 8]).tolist() == [2 * 64 + 1.5 * 9, 0.0, 8 + 1.5]
+    with pytest.raises(ValueError):
+        adapter_load(np.array([1, 2]), [8])
