@@ -119,7 +119,7 @@ class TPLora:
     def apply(self, projs: Sequence[Tuple[torch.Tensor, torch.Tensor, AdapterPool]], layer: int,
               skip_arrival: bool = False) -> None:
         """``projs``: ``(x_shard [T, h_in/tp], y_shard [T, h_out/tp], pool_shard)`` per projection.
-        ``skip_arrival`` (peer exchange only) withholds this rank's arrival signal: a failure made on the
+        ``skip_arrival`` (peer exchange only) withholds this rank's packets: a failure made on the
         host, with which tests check that the peers give up instead of hanging."""
         n = len(projs)
         t = projs[0][0].shape[0]

@@ -175,7 +175,7 @@ int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* off
 enum { B200_LORA_TP_MAX_RANKS = 8, B200_LORA_TP_COUNTER_BYTES = 24576 };
 typedef struct b200_lora_tp {
     void* landing[B200_LORA_TP_MAX_RANKS][2];  /* [r][b]: landing buffer b of rank r as mapped into this process */
-    void* flags[B200_LORA_TP_MAX_RANKS];       /* [r]: rank r's counter block (only that of r == rank is used) */
+    void* flags[B200_LORA_TP_MAX_RANKS];       /* [r]: rank r's counters and hint words (peers write the hints) */
     int32_t tp, rank;
     size_t set_stride;                         /* bytes from the landing buffers of set 0 to those of set 1 */
 } b200_lora_tp;
@@ -193,7 +193,7 @@ int b200_lora_tp_exchange(const b200_lora_tp* tp, void* workspace, int32_t max_t
                           int32_t n_proj, int32_t skip_arrival, void* stream);
 /* b200_lora_apply for a tensor-parallel rank in ONE call: shrink half, exchange, expand half.  `flags` as
  * for b200_lora_apply, without the ONLY_* bits.  Two exchanges run per apply, each with its own landing
- * buffers and arrival words: that of the rows of tall runs between the two tile launches (on a side stream
+ * buffers and counters: that of the rows of tall runs between the two tile launches (on a side stream
  * inside the call), that of all other rows between the BGMV halves; each moves only the rank columns of its
  * rows, and each hides behind the other chain's kernels.  With B200_LORA_NO_TENSOR there is one exchange.
  * All ranks must make the same calls with the same flags on the same plan contents. */
