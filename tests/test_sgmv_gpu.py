@@ -226,3 +226,36 @@ def test_mixed_apply_in_a_cuda_graph_forks_and_joins():
     g.replay()
     torch.cuda.synchronize()
     assert rel_err(y.double().cpu().numpy(), 2 * c.oracle_delta(0)) <= TOL
+
+
+def test_serial_tiles_switch_gives_the_same_bits(tmp_path):
+    """B200_LORA_SERIAL_TILES=1 keeps the tile launches on the caller's stream; the result is the same, bit for bit."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = f"""
+import sys
+sys.path[:0] = [{root!r}, {os.path.join(root, 'tests')!r}]
+import numpy as np, torch
+import ae296_b200 as L
+from lora_testlib import Case
+rng = np.random.default_rng(41)
+ranks = rng.choice([16, 32, 64], 9).astype(np.int32)
+ids = np.concatenate([rng.integers(0, 9, 80), np.repeat([5, 1], [140, 260])]).astype(np.int32)
+c = Case(len(ids), 9, 768, 1024, ranks, "fp16", seed=43, ids=ids)
+y = torch.zeros(c.T, c.h_out, dtype=c.tdt, device="cuda")
+b = L.LoraBatch(c.T, 9, 768, 1).set_ids(c.ids_dev, c.pool, tiles=True)
+for _ in range(3):
+    b.apply([(c.x, y, c.pool)], 0)
+torch.cuda.synchronize()
+b.workspace.check()
+np.save(sys.argv[1], y.float().cpu().numpy())
+"""
+    outs = []
+    for name, extra in (("fork", {}), ("serial", {"B200_LORA_SERIAL_TILES": "1"})):
+        path = str(tmp_path / f"{name}.npy")
+        env = dict(os.environ, **extra)
+        env.pop("B200_LORA_SERIAL_TILES", None) if not extra else None
+        subprocess.run([sys.executable, "-c", script, path], check=True, env=env, timeout=300)
+        outs.append(np.load(path))
+    assert np.abs(outs[0]).max() > 0 and np.array_equal(outs[0], outs[1])
