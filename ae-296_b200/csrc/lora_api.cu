@@ -462,10 +462,10 @@ int b200_lora_workspace_v_region(int32_t max_tokens, int32_t n_proj, size_t* off
 }
 
 // ---- tensor-parallel exchange ---------------------------------------------------------------------
-// one allocation: two sets of two landing buffers [tp][n_proj][max_tokens][64] of 8-byte packets (value,
+// one allocation: two sets of two landing buffers [tp + 1][n_proj][max_tokens][64] of 8-byte packets (value,
 // exchange number), then per set the exchange counter and the CTA counter; everything 256-byte aligned
 static size_t tp_landing_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp) {
-    return (((size_t)tp * n_proj * max_tokens * kMaxRank * 8) + 255) & ~size_t(255);
+    return (((size_t)(tp + 1) * n_proj * max_tokens * kMaxRank * 8) + 255) & ~size_t(255);     // a slot per rank + one for owners' sums
 }
 
 size_t b200_lora_tp_bytes(int32_t max_tokens, int32_t n_proj, int32_t tp) {

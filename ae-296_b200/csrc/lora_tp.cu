@@ -24,6 +24,12 @@
 // number returns to a buffer only after 2^32 exchanges.  No bulk/TMA copy touches peer memory and
 // nothing here uses multicast.
 //
+// Large exchanges over many ranks go through an owner instead (`via_owner`): every group of rows has
+// one owning rank (group number modulo tp); the others send their partial to the owner alone, the
+// owner adds them up in rank order and sends the sum to everybody (a landing slot of its own).  A
+// rank then sends 2 (tp-1)/tp of the data instead of tp-1 times the data, for one more trip over
+// NVLink; the rows of tall runs take this route from four ranks on, everything else stays direct.
+//
 // A tensor-parallel apply runs two such exchanges side by side, one for the rows of tall runs
 // (between the two tile launches, on the side stream) and one for all other rows (between the
 // BGMV halves): each takes its rows and their rank columns from the plan, and each has its own
@@ -31,6 +37,7 @@
 // After the TMA shrink kernel the exchange of the BGMV rows starts from that kernel's split-K
 // slots: it adds them up itself (in slot order, as the expand kernel's producers do), so no
 // kernel stands between the shrink half and the exchange.
+#include <stdlib.h>
 #include <string.h>
 
 #include "lora_common.cuh"
@@ -145,7 +152,7 @@ __device__ __forceinline__ void tp_for_rows(const PlanView& pv, const RowSel& rs
 // kernel of that many CTAs.
 template <typename T>
 __global__ void __launch_bounds__(256) tp_exchange_kernel(const TpArgs a, const __grid_constant__ ApplyParams p, int kind,
-                                                          int all_units, int fold_grid, int skip_push) {
+                                                          int all_units, int fold_grid, int skip_push, int via_owner) {
     pdl_wait_prior();                        // the shrink half's result is complete
     if (threadIdx.x == 0) pdl_launch_dependents();
     const int cap = p.cap, n_tokens = p.n_tokens, n_proj = p.n_proj;
@@ -184,8 +191,9 @@ __global__ void __launch_bounds__(256) tp_exchange_kernel(const TpArgs a, const 
                 v4[idx] = val;
             } else val = v4[idx];
             if (skip_push) return;
+            const int owner = via_owner ? unit % a.tp : -1;
             for (int s = 0; s < a.tp; ++s) {
-                if (s == a.rank) continue;
+                if (s == a.rank || (via_owner && s != owner)) continue;
                 uint4* dst = a.peer_landing[s][buf] + ((size_t)a.rank * slot_f4 + idx) * 2;
                 st_packet(dst, 0, val.x, epoch);
                 st_packet(dst, 1, val.y, epoch);
@@ -207,7 +215,21 @@ __global__ void __launch_bounds__(256) tp_exchange_kernel(const TpArgs a, const 
     __syncthreads();
     // ---- gather: read the own landing buffer until the packets are this exchange's, add in rank order ----
     bool gave_up = false;
-    tp_for_rows(pv, rs, [&](size_t idx, int, int, int) {
+    // one float4 = two packet pairs at `src`; polls until all four packets are this exchange's
+    auto wait4 = [&](const uint4* src, uint4 p0, uint4 p1, unsigned nap) {
+        for (unsigned i = 0; !gave_up && (p0.y != epoch || p0.w != epoch || p1.y != epoch || p1.w != epoch); ++i) {
+            if (i >= kTpSpinLimit || ((i & 0xffu) == 0xffu && *reinterpret_cast<volatile unsigned*>(err) != 0u)) {
+                gave_up = true;                                           // this thread stops waiting for anything
+                break;
+            }
+            if (i > 16 || nap > 64) __nanosleep(nap);
+            p0 = ld_packets(src);
+            p1 = ld_packets(src + 1);
+        }
+        return make_float4(__uint_as_float(p0.x), __uint_as_float(p0.z), __uint_as_float(p1.x), __uint_as_float(p1.z));
+    };
+    tp_for_rows(pv, rs, [&](size_t idx, int, int unit, int) {
+        if (via_owner && unit % a.tp != a.rank) return;                   // somebody else adds this group up
         const float4 own = v4[idx];
         const uint4* mine = a.peer_landing[a.rank][buf] + idx * 2;
         uint4 pk[kTpMaxRanks][2];                                         // every peer's packets requested before any is looked at
@@ -222,24 +244,26 @@ __global__ void __launch_bounds__(256) tp_exchange_kernel(const TpArgs a, const 
         for (int s = 0; s < kTpMaxRanks; ++s) {                           // rank order: the same sum on every rank
             if (s >= a.tp) continue;
             float4 x = own;
-            if (s != a.rank) {
-                const uint4* src = mine + (size_t)s * slot_f4 * 2;
-                uint4 p0 = pk[s][0], p1 = pk[s][1];
-                for (unsigned i = 0; !gave_up && (p0.y != epoch || p0.w != epoch || p1.y != epoch || p1.w != epoch); ++i) {
-                    if (i >= kTpSpinLimit || ((i & 0xffu) == 0xffu && *reinterpret_cast<volatile unsigned*>(err) != 0u)) {
-                        gave_up = true;                                   // this thread stops waiting for anything
-                        break;
-                    }
-                    if (i > 16) __nanosleep(64);
-                    p0 = ld_packets(src);
-                    p1 = ld_packets(src + 1);
-                }
-                x = make_float4(__uint_as_float(p0.x), __uint_as_float(p0.z), __uint_as_float(p1.x), __uint_as_float(p1.z));
-            }
+            if (s != a.rank) x = wait4(mine + (size_t)s * slot_f4 * 2, pk[s][0], pk[s][1], 64);
             acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
         }
         v4[idx] = acc;
+        if (via_owner && !skip_push)                                      // the sum goes out to everybody's slot number tp
+            for (int s = 0; s < a.tp; ++s) {
+                if (s == a.rank) continue;
+                uint4* dst = a.peer_landing[s][buf] + ((size_t)a.tp * slot_f4 + idx) * 2;
+                st_packet(dst, 0, acc.x, epoch);
+                st_packet(dst, 1, acc.y, epoch);
+                st_packet(dst + 1, 0, acc.z, epoch);
+                st_packet(dst + 1, 1, acc.w, epoch);
+            }
     });
+    if (via_owner)                                                        // the groups other ranks own: their sums
+        tp_for_rows(pv, rs, [&](size_t idx, int, int unit, int) {
+            if (unit % a.tp == a.rank) return;
+            const uint4* src = a.peer_landing[a.rank][buf] + ((size_t)a.tp * slot_f4 + idx) * 2;
+            v4[idx] = wait4(src, ld_packets(src), ld_packets(src + 1), 200);
+        });
     if (gave_up) atomicMax(err, 8u);
     // ---- the last CTA to get here advances the exchange counter ----
     __syncthreads();
@@ -272,8 +296,11 @@ cudaError_t launch_exchange(int io_dtype, int grid, cudaStream_t s, Args&&... ar
 cudaError_t launch_tp_exchange_rows(const b200_lora_tp* tp, int set, bool tall, bool all_units, const ApplyParams& p, int fold_grid,
                                     int io_dtype, int skip_push, int n_sm, cudaStream_t s) {
     const TpArgs a = tp_args(tp, set);
+    // B200_LORA_TP_VIA_OWNER=0/1 in the environment overrides the route (for tests on two GPUs)
+    static const int forced = [] { const char* v = getenv("B200_LORA_TP_VIA_OWNER"); return v ? (v[0] == '1' ? 1 : 0) : -1; }();
+    const int via_owner = forced >= 0 ? forced : (tall && tp->tp >= 4) ? 1 : 0;
     return launch_exchange(io_dtype, exchange_grid(p.n_tokens, p.n_proj, n_sm), s, a, p, tall ? 2 : 1, all_units ? 1 : 0,
-                           tall ? 0 : fold_grid, skip_push);
+                           tall ? 0 : fold_grid, skip_push, via_owner);
 }
 
 cudaError_t launch_tp_exchange(const b200_lora_tp* tp, void* workspace, int n_proj, int cap, int n_tokens, int skip_push,
@@ -285,7 +312,7 @@ cudaError_t launch_tp_exchange(const b200_lora_tp* tp, void* workspace, int n_pr
     p.cap = cap;
     p.n_tokens = n_tokens;
     p.workspace = workspace;
-    return launch_exchange(B200_LORA_BF16, exchange_grid(n_tokens, n_proj, n_sm), s, a, p, 0, 0, 0, skip_push);
+    return launch_exchange(B200_LORA_BF16, exchange_grid(n_tokens, n_proj, n_sm), s, a, p, 0, 0, 0, skip_push, 0);
 }
 
 }  // namespace b200lora
