@@ -129,8 +129,11 @@ def _spawn(world, **kw):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tplora_peer_exchange_matches_oracle_column_slices():
-    """The library's own exchange over peer memory instead of the NCCL all-reduce."""
+@pytest.mark.parametrize("via_owner", ["0", "1"])
+def test_tplora_peer_exchange_matches_oracle_column_slices(via_owner, monkeypatch):
+    """The library's own exchange over peer memory instead of the NCCL all-reduce: every rank sending to every
+    rank, and the route through an owning rank that large exchanges take from four ranks on (forced here)."""
+    monkeypatch.setenv("B200_LORA_TP_VIA_OWNER", via_owner)     # read once per process: the spawned ranks inherit it
     res = _spawn(2, exchange="peer")
     assert set(res) == {0, 1} and max(res.values()) <= 2e-3, res
 
