@@ -196,6 +196,8 @@ int b200_lora_tp_exchange(const b200_lora_tp* tp, void* workspace, int32_t max_t
  * buffers and counters: that of the rows of tall runs between the two tile launches (on a side stream
  * inside the call), that of all other rows between the BGMV halves; each moves only the rank columns of its
  * rows, and each hides behind the other chain's kernels.  With B200_LORA_NO_TENSOR there is one exchange.
+ * From four ranks on the tall rows' exchange goes through an owning rank per group of rows (partials to the
+ * owner, its sum to everybody); B200_LORA_TP_VIA_OWNER=0/1 in the environment forces either route.
  * All ranks must make the same calls with the same flags on the same plan contents. */
 int b200_lora_apply_tp(const b200_lora_proj* projs, int32_t n_proj, const b200_lora_adapters* adapters,
                        const void* plan, int32_t max_tokens, int32_t n_tokens, int32_t layer, int32_t io_dtype,
