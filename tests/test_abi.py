@@ -65,3 +65,38 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libb200lora.so")
     with pytest.raises(ImportError):
         _lib.lib()
+
+
+def test_tensor_parallel_entry_points_check_their_arguments(lib):
+    """Host-only parts of the tensor-parallel ABI: buffer size, layout arithmetic, argument checks."""
+    from ae296_b200._lib import Adapters, Proj, TpContext
+    assert lib.b200_lora_tp_bytes(256, 3, 1) == 0 and lib.b200_lora_tp_bytes(256, 3, 9) == 0      # 2..8 ranks
+    assert lib.b200_lora_tp_bytes(256, 5, 2) == 0
+    # two sets of two landing buffers of (tp + 1) slots of 8-byte packets, then the counter block
+    slot = 3 * 256 * 64 * 8
+    assert lib.b200_lora_tp_bytes(256, 3, 4) == 4 * 5 * slot + 24576
+    ctx = TpContext()
+    ctx.tp, ctx.rank = 4, 1
+    base = 1 << 30
+    for r in range(4):
+        assert lib.b200_lora_tp_layout(C.byref(ctx), r, C.c_void_p(base * (r + 1)), 256, 3) == 0
+        assert ctx.landing[r][0] == base * (r + 1) and ctx.landing[r][1] == base * (r + 1) + 5 * slot
+        assert ctx.flags[r] == base * (r + 1) + 4 * 5 * slot
+    assert ctx.set_stride == 2 * 5 * slot
+    assert lib.b200_lora_tp_layout(C.byref(ctx), 8, C.c_void_p(base), 256, 3) == -2
+    assert lib.b200_lora_tp_layout(None, 0, C.c_void_p(base), 256, 3) == -1
+    ad = Adapters(None, None, None, 4, 2, 16, 0, 1.0, 0, 0)
+    pj = (Proj * 1)(Proj(256, 256, 256, 256, 128, 128, 128, 128))
+    big = 1 << 30
+    args = (pj, 1, C.byref(ad), C.c_void_p(256), 8, 8, 0, 0, 0)
+    assert lib.b200_lora_apply_tp(*args, 0, C.c_void_p(256), big, None, 0, None) == -1          # no context
+    from ae296_b200 import _lib
+    for half in (_lib.ONLY_SHRINK, _lib.ONLY_EXPAND):                                               # the call runs both halves itself
+        assert lib.b200_lora_apply_tp(*args, half, C.c_void_p(256), big, C.byref(ctx), 0, None) == -2
+    one = TpContext()
+    one.tp, one.rank = 1, 0
+    assert lib.b200_lora_apply_tp(*args, 0, C.c_void_p(256), big, C.byref(one), 0, None) == -2    # fewer than two ranks
+    hole = TpContext()
+    hole.tp, hole.rank, hole.set_stride = 2, 0, 1024
+    assert lib.b200_lora_apply_tp(*args, 0, C.c_void_p(256), big, C.byref(hole), 0, None) == -2   # unmapped peers
+    assert lib.b200_lora_tp_exchange(C.byref(hole), C.c_void_p(256), 8, 8, 1, 0, None) == -1
